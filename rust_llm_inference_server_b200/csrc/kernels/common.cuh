@@ -1,0 +1,75 @@
+// Shared helpers for the sm_100a kernels: element conversion, 16-byte loads, warp reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Element type codes used by every exported launcher.
+#define RLIS_F32 0
+#define RLIS_BF16 1
+
+// Error codes returned by launchers in addition to cudaError_t values (which are positive).
+#define RLIS_ERR_UNSUPPORTED (-1)
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Number of elements of T in one 16-byte vector.
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+// Loads 16 bytes from a 16-byte aligned address and widens them to float.
+template <typename T> __device__ __forceinline__ void load16(const T* p, float* out);
+template <> __device__ __forceinline__ void load16<float>(const float* p, float* out) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <> __device__ __forceinline__ void load16<bf16>(const bf16* p, float* out) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float s = lane < nwarps ? scratch[lane] : 0.f;
+        s = warp_sum(s);
+        if (lane == 0) scratch[32] = s;
+    }
+    __syncthreads();
+    float r = scratch[32];
+    __syncthreads();
+    return r;
+}
+
+#define RLIS_LAUNCH_CHECK() ((int)cudaGetLastError())

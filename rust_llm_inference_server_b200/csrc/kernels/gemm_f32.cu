@@ -1,0 +1,65 @@
+// True 32-bit matrix product for the float32 path: C[M, N] = A[M, K] * W[N, K]^T with FFMA on the
+// CUDA cores (no TF32, no tensor cores).  Every output element is accumulated over k = 0..K-1 in
+// that order, whatever M, N or the tile it falls in, so a row's result does not depend on what
+// else is in the batch.  Role in the reference: `x.matmul(w.t())`, crates/model/src/layers.rs:82.
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 16;
+
+__global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__ A,
+                                                       const float* __restrict__ W,
+                                                       float* __restrict__ C, int M, int N, int K) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += 256) {
+            const int r = i / BK, c = i % BK;
+            const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+            As[c][r] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.f;
+            Ws[c][r] = (gn < N && gk < K) ? W[(size_t)gn * K + gk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty * 4 + i;
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn < N) C[(size_t)gm * N + gn] = acc[i][j];
+        }
+    }
+}
+}  // namespace
+
+extern "C" int rlis_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K,
+                                cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
+    sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K);
+    return RLIS_LAUNCH_CHECK();
+}

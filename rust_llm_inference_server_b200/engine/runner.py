@@ -1,0 +1,198 @@
+"""The step function: one batch of (request, its next tokens), portions of prompts beside single
+decoded tokens, run from the cache; logits at the wanted places.
+
+Role of `Engine::step` + `Llama::forward_batch` + `PagedBatch::new`
+(crates/engine/src/engine.rs:617-726, crates/model/src/llama.rs:218-286,
+crates/model/src/paged.rs:256-296).  Differences by design: logits only where they are asked for
+(the reference runs its LM head on every sequence's last row, llama.rs:279-285), and one upload
+of all index arrays per step.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import ops
+
+
+class StepError(ValueError):
+    """A batch the step function refuses before anything is launched."""
+
+
+@dataclass
+class StepEntry:
+    seq_id: int
+    tokens: list                    # the request's next tokens (at least one)
+    start_pos: int                  # how many of its tokens are already in the cache
+    want: list = field(default_factory=list)   # places among `tokens` whose logits are wanted
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepContext:
+    """Index arrays of one step on the device, and the step's scratch buffers."""
+
+    def __init__(self, runner, n_tokens: int, n_seqs: int):
+        self._runner = runner
+        self.n_tokens = n_tokens
+        self.n_seqs = n_seqs
+        self.token_ids = self.positions = self.seq_of_token = None
+        self.slots: list = []
+        self.block_tables: list = []
+        self.ctx_lens = self.cu_seqlens = self.state_slots = self.logit_rows = None
+        self.q_lens: list = []
+        self.starts: list = []
+        self.max_q_len = 0
+        self.max_ctx_len = 0
+        self.all_decode = False
+
+    def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        return self._runner.workspace(name, shape, dtype)
+
+
+class ModelRunner:
+    def __init__(self, model, cache_manager, storage, max_seq_len: int):
+        self.model = model
+        self.cache = cache_manager
+        self.storage = storage
+        self.device = model.device
+        self.max_seq_len = int(max_seq_len)
+        self.groups = storage.groups
+        self.max_blocks = max(1, max((self.max_seq_len + g.page_size - 1) // g.page_size for g in self.groups)) \
+            if self.groups else 1
+        self._caches = [storage.layer_cache(c) for c in range(len(model.cache_slot_specs))]
+        self._states = storage.states
+        self._ws: dict[str, torch.Tensor] = {}
+        self._meta_host = None
+        self._meta_dev = None
+        self._graph_keepalive: list = []
+        self._upload_done = None
+
+    # ---- scratch memory that keeps its address while it is large enough ----
+
+    def workspace(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._ws.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            cap = max(n, 2 * buf.numel() if buf is not None and buf.dtype == dtype else n)
+            if buf is not None:
+                self._graph_keepalive.append(buf)
+            buf = torch.empty((cap,), dtype=dtype, device=self.device)
+            self._ws[name] = buf
+        return buf[:n].view(*shape)
+
+    def _meta(self, n: int):
+        if self._meta_host is None or self._meta_host.numel() < n:
+            cap = max(n, 1 << 16)
+            if self._meta_dev is not None:
+                self._graph_keepalive.append(self._meta_dev)
+            self._meta_host = torch.empty((cap,), dtype=torch.int32, pin_memory=True)
+            self._meta_dev = torch.empty((cap,), dtype=torch.int32, device=self.device)
+        return self._meta_host, self._meta_dev
+
+    # ---- the step ----
+
+    def prepare(self, entries: list) -> StepContext:
+        """Checks the batch and uploads its index arrays (one copy)."""
+        if not entries:
+            raise StepError("empty batch")
+        B = len(entries)
+        G = len(self.groups)
+        ids, starts, lens = [], [], []
+        seen = set()
+        want_rows = []
+        T = 0
+        V = self.model.spec.vocab_size
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.seq_id}: empty sequence in batch")
+            if e.seq_id in seen:
+                raise StepError(f"request {e.seq_id} appears twice in one batch")
+            seen.add(e.seq_id)
+            if e.start_pos < 0 or e.start_pos + n > self.max_seq_len:
+                raise StepError(f"request {e.seq_id}: sequence of {e.start_pos + n} positions exceeds "
+                                f"max_seq_len {self.max_seq_len}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"request {e.seq_id}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(T + w)
+            ids.append(int(e.seq_id))
+            starts.append(int(e.start_pos))
+            lens.append(n)
+            T += n
+        W = len(want_rows)
+        mb = self.max_blocks
+        # layout of the int32 block: see the offsets below; every region starts 16-byte aligned
+        o_tok = 0
+        o_pos = o_tok + _align4(T)
+        o_sot = o_pos + _align4(T)
+        o_slots = o_sot + _align4(T)
+        Ta = _align4(T)
+        o_ctx = o_slots + G * Ta
+        o_cu = o_ctx + _align4(B)
+        o_ss = o_cu + _align4(B + 1)
+        o_rows = o_ss + _align4(B)
+        o_bt = o_rows + _align4(max(W, 1))
+        total = o_bt + G * B * mb
+        host, dev = self._meta(total)
+        if self._upload_done is not None:
+            self._upload_done.synchronize()   # the last step's upload has left the pinned block
+        h = host.numpy()
+        tok = h[o_tok:o_tok + T]
+        k = 0
+        for e in entries:
+            n = len(e.tokens)
+            tok[k:k + n] = e.tokens
+            k += n
+        if T and (int(tok.min()) < 0 or int(tok.max()) >= V):
+            raise StepError(f"token id outside the vocabulary of {V}")
+        try:
+            self.cache.pack_step(
+                ids, starts, lens, h[o_pos:o_pos + T], h[o_sot:o_sot + T],
+                h[o_slots:o_slots + G * Ta].reshape(G, Ta), h[o_bt:o_bt + G * B * mb].reshape(G, B, mb),
+                h[o_ctx:o_ctx + B], h[o_cu:o_cu + B + 1], h[o_ss:o_ss + B])
+        except RuntimeError as err:
+            raise StepError(str(err)) from None
+        if W:
+            h[o_rows:o_rows + W] = want_rows
+        dev[:total].copy_(host[:total], non_blocking=True)
+        if self._upload_done is None:
+            self._upload_done = torch.cuda.Event()
+        self._upload_done.record()
+
+        st = StepContext(self, T, B)
+        st.token_ids = dev[o_tok:o_tok + T]
+        st.positions = dev[o_pos:o_pos + T]
+        st.seq_of_token = dev[o_sot:o_sot + T]
+        st.slots = [dev[o_slots + g * Ta:o_slots + g * Ta + T] for g in range(G)]
+        st.block_tables = [dev[o_bt + g * B * mb:o_bt + (g + 1) * B * mb].view(B, mb) for g in range(G)]
+        st.ctx_lens = dev[o_ctx:o_ctx + B]
+        st.cu_seqlens = dev[o_cu:o_cu + B + 1]
+        st.state_slots = dev[o_ss:o_ss + B]
+        st.logit_rows = dev[o_rows:o_rows + W] if W else None
+        st.q_lens = lens
+        st.starts = starts
+        st.seq_ids = ids
+        st.max_q_len = max(lens)
+        st.max_ctx_len = max(s + n for s, n in zip(starts, lens))
+        st.all_decode = st.max_q_len == 1
+        st.h2d_bytes = total * 4
+        return st
+
+    def forward(self, st: StepContext):
+        """Launches the model on a prepared step; float32 logits [wanted, vocab] or None."""
+        resid, delta = self.model.forward(st, self._caches, self._states)
+        if st.logit_rows is None:
+            return None
+        return self.model.logits(resid, delta, st, st.logit_rows)
+
+    def step(self, entries: list):
+        return self.forward(self.prepare(entries))

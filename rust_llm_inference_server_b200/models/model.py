@@ -1,0 +1,132 @@
+"""A model built from a ModelSpec: embedding, blocks in their run order, final norm, LM head.
+
+Role of `Llama::{new, hidden, forward_batch}` (crates/model/src/llama.rs:142-286), with the
+architecture taken out: this class reads only the spec.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.model_config import read_config_json
+from ..config.registry import lookup_architecture
+from ..parts.base import build_block, build_norm
+from ..parts.spec import ModelSpec
+from ..weights.loader import PlacedSource, check_checkpoint
+from ..weights.safetensors_io import Checkpoint, open_model_dir
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "f32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute type must be bfloat16 or float32, got {name}")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"compute type must be bfloat16 or float32, got {name!r}") from None
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.blocks = [build_block(ls, dtype, self.device) for ls in spec.layers]
+        self.final_norm = build_norm(spec.final_norm, dtype, self.device)
+        self.calls = tuple(spec.order)
+        self.embed = None
+        self.lm_head = None
+        self._plan_caches()
+
+    # ---- what the cache manager has to provide ----
+
+    def _plan_caches(self) -> None:
+        """Per cache slot its KVCacheSpec (from the call that writes it); per call its StateSpec."""
+        slots: dict[int, object] = {}
+        writer: dict[int, int] = {}
+        self.call_state_specs = []
+        for ci, call in enumerate(self.calls):
+            if not 0 <= call.layer < len(self.blocks):
+                raise ValueError(f"run order names layer {call.layer}; the model has {len(self.blocks)}")
+            mixer = self.blocks[call.layer].mixer
+            cs = mixer.cache_spec()
+            if call.writes_cache:
+                if call.cache in writer:
+                    raise ValueError(f"cache slot {call.cache} is written by calls {writer[call.cache]} and {ci}")
+                writer[call.cache] = ci
+                slots[call.cache] = cs
+            else:
+                if call.cache not in writer:
+                    raise ValueError(f"call {ci} reads cache slot {call.cache} before any call has written it")
+                if slots[call.cache] != cs:
+                    raise ValueError(f"call {ci} reads cache slot {call.cache} whose geometry {slots[call.cache]} "
+                                     f"differs from its own {cs}")
+            self.call_state_specs.append(mixer.state_spec())
+        n = (max(slots) + 1) if slots else 0
+        self.cache_slot_specs = [slots.get(i) for i in range(n)]
+
+    # ---- weights ----
+
+    def tensors(self) -> dict:
+        out = {self.spec.embedding: (self.spec.vocab_size, self.spec.hidden),
+               self.spec.lm_head: (self.spec.vocab_size, self.spec.hidden)}
+        for blk in self.blocks:
+            for part in blk.parts():
+                for name, shape in part.tensors().items():
+                    if name in out and tuple(out[name]) != tuple(shape):
+                        raise ValueError(f"tensor {name} is expected with shapes {out[name]} and {shape}")
+                    out[name] = tuple(shape)
+        out.update(self.final_norm.tensors())
+        return out
+
+    def load(self, ckpt: Checkpoint) -> None:
+        check_checkpoint(self.tensors(), ckpt, self.spec.ignorable)
+        src = PlacedSource(ckpt, self.dtype, self.device)
+        self.embed = src.get(self.spec.embedding).contiguous()
+        self.lm_head = self.embed if self.spec.lm_head == self.spec.embedding \
+            else src.get(self.spec.lm_head).contiguous()
+        for blk in self.blocks:
+            for part in blk.parts():
+                part.load(src)
+        self.final_norm.load(src)
+
+    # ---- forward ----
+
+    def forward(self, step, caches, states):
+        """Runs the step's tokens through every call of the run order.  Returns the float32
+        residual stream and the last pending delta; `logits` finishes chosen rows."""
+        T = step.n_tokens
+        resid = step.buffer("resid", (T, self.spec.hidden), torch.float32)
+        ops.embedding(step.token_ids, self.embed, resid)
+        delta = None
+        for ci, call in enumerate(self.calls):
+            blk = self.blocks[call.layer]
+            resid, delta = blk.forward(resid, delta, step, caches[call.cache], states[ci], call.writes_cache)
+        return resid, delta
+
+    def logits(self, resid, delta, step, rows: torch.Tensor):
+        """Final norm and LM head on the rows in `rows` (int32 indices into the step's tokens):
+        float32 logits [len(rows), vocab] (crates/model/src/llama.rs:272-285)."""
+        h = self.final_norm.forward_rows(resid, delta, step, rows)
+        return ops.linear(h, self.lm_head, out_dtype=torch.float32)
+
+
+def build_model(config_json: dict, dtype, device="cuda") -> Model:
+    arch = lookup_architecture(config_json)
+    cfg = arch.parse_config(config_json)
+    model = Model(arch.describe(cfg), parse_dtype(dtype), device)
+    model.config = cfg
+    model.architecture = arch.name
+    return model
+
+
+def load_model(model_dir: str, dtype="bfloat16", device="cuda") -> Model:
+    """Reads config.json, picks the architecture through the registry, loads the weights."""
+    model = build_model(read_config_json(model_dir), dtype, device)
+    model.load(open_model_dir(model_dir))
+    return model

@@ -1,0 +1,213 @@
+"""The hot ops of the forward pass: thin, checked wrappers over the sm_100a kernels.
+
+Every function takes CUDA tensors, checks element types, shapes and contiguity, and launches on
+the current stream.  A size that a kernel does not take is refused with an error; nothing here
+falls back to a tensor library's model code or to the CPU.  Matrix products in bfloat16 go to the
+library GEMM (cuBLAS through `torch.mm`), as the reference's go to its tensor library
+(crates/model/src/layers.rs:82); in float32 they go to this package's own FFMA kernel so that
+no reduced-precision matrix mode can enter.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .library import KernelError, check, lib
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+# Number of launches of this package's kernels since the last reset (a claim the benchmark
+# reports; launches replayed from a captured graph are counted by the graph's owner).
+launch_count = 0
+
+
+def _code(dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"element type {dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _req(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: expected a contiguous tensor, got strides {t.stride()}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if shape is not None:
+        if t.dim() != len(shape) or any(s is not None and s != g for s, g in zip(shape, t.shape)):
+            raise KernelError(f"{name}: expected shape {shape}, got {tuple(t.shape)}")
+
+
+def _count() -> None:
+    global launch_count
+    launch_count += 1
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to float32.  ids int32 [T]; out float32 [T, H]."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _req(ids, "ids", torch.int32, (T,))
+    _req(table, "table")
+    _req(out, "out", torch.float32, (T, H))
+    check(lib().rlis_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, H, V,
+                               _code(table.dtype), _stream()), "embedding")
+    _count()
+    return out
+
+
+def rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """If `delta` is given: resid += delta (float32).  out = rmsnorm(resid) * weight, rounded once.
+
+    resid float32 [T, H] (updated in place), weight float32 [H], out and delta in the activation
+    type.  With `rows` (int32 [R]): out [R, H] is computed from rows resid[rows] (+ delta[rows])
+    and resid is left unchanged."""
+    T, H = resid.shape
+    _req(resid, "resid", torch.float32)
+    _req(weight, "weight", torch.float32, (H,))
+    n_out = T
+    if rows is not None:
+        _req(rows, "rows", torch.int32, (None,))
+        n_out = rows.shape[0]
+    _req(out, "out", None, (n_out, H))
+    if delta is not None:
+        _req(delta, "delta", out.dtype, (T, H))
+    check(lib().rlis_rmsnorm(resid.data_ptr(), delta.data_ptr() if delta is not None else None,
+                             weight.data_ptr(), out.data_ptr(),
+                             rows.data_ptr() if rows is not None else None, n_out, H, float(eps),
+                             _code(out.dtype), _stream()), "rmsnorm")
+    _count()
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I]."""
+    T, I2 = gate_up.shape
+    if I2 % 2:
+        raise KernelError(f"swiglu: the fused gate|up width must be even, got {I2}")
+    _req(gate_up, "gate_up")
+    _req(out, "out", gate_up.dtype, (T, I2 // 2))
+    check(lib().rlis_swiglu(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, _code(out.dtype),
+                            _stream()), "swiglu")
+    _count()
+    return out
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FFMA, fixed order over K)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _req(a, "a", torch.float32)
+    _req(w, "w", torch.float32, (N, K))
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _req(out, "out", torch.float32, (M, N))
+    check(lib().rlis_gemm_f32_nt(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _stream()),
+          "gemm_f32")
+    _count()
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: the
+    library GEMM with float32 accumulation; `out_dtype=torch.float32` keeps the accumulator's
+    precision (used for logits)."""
+    if x.dtype == torch.float32:
+        return gemm_f32(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: expected matching float32 or bfloat16 operands, got {x.dtype}, {w.dtype}")
+    if not x.is_cuda:
+        raise KernelError("linear: expected CUDA tensors; there is no CPU path")
+    if out_dtype is None or out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+               v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
+               inv_freq: torch.Tensor | None, n_heads: int, n_kv_heads: int, head_dim: int,
+               page_size: int) -> torch.Tensor:
+    """Rotates q and k by their positions and stores k, v at `slots` of one layer's paged cache.
+
+    qkv [T, (nh + 2 nkv) d]; q_out [T, nh d]; caches [pages, nkv, page_size, d]; positions and
+    slots int32 [T] (slots None: nothing is stored); inv_freq float32 [d/2] (None: no rotation)."""
+    T = qkv.shape[0]
+    _req(qkv, "qkv", None, (T, (n_heads + 2 * n_kv_heads) * head_dim))
+    _req(q_out, "q_out", qkv.dtype, (T, n_heads * head_dim))
+    _req(positions, "positions", torch.int32, (T,))
+    if slots is not None:
+        _req(slots, "slots", torch.int32, (T,))
+        for c, nm in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+            _req(c, nm, qkv.dtype, (None, n_kv_heads, page_size, head_dim))
+    if inv_freq is not None:
+        _req(inv_freq, "inv_freq", torch.float32, (head_dim // 2,))
+    check(lib().rlis_rope_cache(
+        qkv.data_ptr(), q_out.data_ptr(),
+        k_cache.data_ptr() if slots is not None else None,
+        v_cache.data_ptr() if slots is not None else None,
+        positions.data_ptr(), slots.data_ptr() if slots is not None else None,
+        inv_freq.data_ptr() if inv_freq is not None else None,
+        T, n_heads, n_kv_heads, head_dim, page_size, _code(qkv.dtype), _stream()), "rope_cache")
+    _count()
+    return q_out
+
+
+def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      out: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
+                      block_tables: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                      page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal grouped-query attention over paged keys and values for any mix of query lengths.
+
+    q, out [T, nh d]; caches [pages, nkv, page_size, d]; seq_of_token, positions int32 [T];
+    block_tables int32 [B, max_blocks].  window 0 = all earlier keys."""
+    T = q.shape[0]
+    _req(q, "q", None, (T, n_heads * head_dim))
+    _req(out, "out", q.dtype, (T, n_heads * head_dim))
+    _req(k_cache, "k_cache", q.dtype, (None, n_kv_heads, page_size, head_dim))
+    _req(v_cache, "v_cache", q.dtype, (None, n_kv_heads, page_size, head_dim))
+    _req(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _req(positions, "positions", torch.int32, (T,))
+    _req(block_tables, "block_tables", torch.int32, (None, None))
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head sizes are multiples of 16 up to 256, got {head_dim}")
+    if n_heads % n_kv_heads:
+        raise KernelError(f"attention: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
+    check(lib().rlis_attention_generic(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        seq_of_token.data_ptr(), positions.data_ptr(), block_tables.data_ptr(),
+        block_tables.shape[1], T, n_heads, n_kv_heads, head_dim, page_size, float(scale),
+        int(window), _code(q.dtype), _stream()), "attention_generic")
+    _count()
+    return out
+
+
+def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_heads: int,
+              head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of every token of the step over its request's cached keys, by the kernel that
+    fits the step (the choice never changes the result beyond rounding)."""
+    return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
+                             step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size,
+                             scale, window)
+
+
+def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token id per row of float32 logits [R, V].  params int32 [R, 2] = (key, bits of 1/T);
+    (0, 0) is greedy.  Returns int32 [R]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise KernelError("sample_rows: logits must be float32 CUDA rows with unit stride")
+    _req(params, "params", torch.int32, (R, 2))
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _req(out, "out", torch.int32, (R,))
+    check(lib().rlis_sample_rows(logits.data_ptr(), params.data_ptr(), out.data_ptr(), R, V,
+                                 logits.stride(0), _stream()), "sample_rows")
+    _count()
+    return out

@@ -1,0 +1,70 @@
+"""Loads the kernel library and declares the C signature of every exported launcher.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA device is present, the
+first op raises.  Launchers return 0, a cudaError_t (> 0) or a negative library code.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from . import build
+
+_lib = None
+
+P = c_void_p
+I = c_int
+F = c_float
+LL = c_longlong
+
+# name -> argument types (the stream is always last)
+SIGNATURES = {
+    "rlis_embedding": [P, P, P, I, I, I, I, P],
+    "rlis_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
+    "rlis_swiglu": [P, P, I, I, I, P],
+    "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
+    "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "rlis_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "rlis_sample_rows": [P, P, P, I, I, LL, P],
+}
+
+OPTIONAL_SIGNATURES: dict = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = build.build_kernels()
+        try:
+            handle = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from e
+        for name, args in {**SIGNATURES, **OPTIONAL_SIGNATURES}.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError as e:
+                raise KernelError(f"kernel library {path} lacks symbol {name}") from e
+            fn.argtypes = args
+            fn.restype = c_int
+        _lib = handle
+    return _lib
+
+
+_CUDA_ERRORS = {1: "invalid value", 2: "out of memory", 9: "invalid configuration",
+                98: "invalid device function", 209: "no kernel image for this device",
+                700: "illegal address", 715: "illegal instruction", 719: "launch failure"}
+
+
+def check(code: int, name: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{name}: this kernel does not take these sizes or this element type")
+    if code < 0:
+        raise KernelError(f"{name}: library error {code}")
+    raise KernelError(f"{name}: CUDA error {code} ({_CUDA_ERRORS.get(code, 'see cudaError_t')})")

@@ -1,0 +1,151 @@
+"""Interfaces of the parts a layer is made of, and the registries that build them from specs.
+
+A part gets its sizes and constants from its spec, names the checkpoint tensors it needs, and
+knows nothing of the model it sits in.  A new kind of part is one class and one `register_*` call.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+
+class TensorSource:
+    """What a part loads from: `get(name, role)` returns the tensor on the device.
+
+    role "matrix": a matrix-product operand, in the compute type (bfloat16 or float32);
+    role "vector": a norm weight or other small float table, widened exactly to float32;
+    role "index":  an integer table, as int32;
+    role "stored": whatever the checkpoint holds, unchanged (32-bit stays 32-bit)."""
+
+    def get(self, name: str, role: str = "matrix") -> torch.Tensor:  # pragma: no cover
+        raise NotImplementedError
+
+
+class Part:
+    def tensors(self) -> dict:
+        """Checkpoint tensors this part reads: {name: shape}."""
+        return {}
+
+    def load(self, src: TensorSource) -> None:
+        pass
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """What a mixer keeps per token: keys and values of `n_kv_heads` heads of `head_dim`, of all
+    earlier tokens (window None) or of the last `window` tokens."""
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size (shape per request, element type)."""
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """One cache slot's device storage as a mixer sees it."""
+    k: torch.Tensor                  # [pages, n_kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    group: int                       # index into the step's block tables and slot lists
+    page_size: int
+
+
+class Mixer(Part):
+    """Token mixing over a request's earlier tokens.  `forward` gets the normed activations
+    [T, hidden] of all tokens of the step and returns [T, hidden] in the same element type."""
+
+    def cache_spec(self) -> Optional[KVCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, step, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor], writes_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    """`forward(resid, delta)`: adds `delta` (or nothing) into the float32 residual stream in
+    place and returns the normed activations in the compute type."""
+
+    def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], step) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_rows(self, resid, delta, step, rows: torch.Tensor) -> torch.Tensor:
+        """The same for the rows `rows` only (the places whose logits are wanted)."""
+        return self.forward(resid, delta, step).index_select(0, rows.long())
+
+
+class PositionEncoding(Part):
+    """Belongs to a mixer.  `encode_and_store` splits the fused q|k|v rows, encodes positions into
+    q and k, writes q to `q_out` and k, v into the paged cache at the step's slots."""
+
+    def encode_and_store(self, qkv, q_out, cache: Optional[LayerCache], step, n_heads: int,
+                         n_kv_heads: int, head_dim: int, store: bool) -> None:
+        raise NotImplementedError
+
+
+_MIXERS: dict[str, Callable] = {}
+_FEED_FORWARDS: dict[str, Callable] = {}
+_NORMS: dict[str, Callable] = {}
+_POSITIONS: dict[str, Callable] = {}
+_ARRANGEMENTS: dict[str, Callable] = {}
+
+
+def _register(table: dict, what: str):
+    def reg(kind: str, factory: Callable, replace: bool = False) -> None:
+        if kind in table and not replace:
+            raise ValueError(f"{what} kind {kind!r} is already registered")
+        table[kind] = factory
+    return reg
+
+
+register_mixer = _register(_MIXERS, "mixer")
+register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
+register_norm = _register(_NORMS, "norm")
+register_position = _register(_POSITIONS, "position encoding")
+register_arrangement = _register(_ARRANGEMENTS, "block arrangement")
+
+
+def _build(table: dict, what: str, spec, dtype, device):
+    kind = getattr(spec, "kind", None)
+    if kind not in table:
+        raise ValueError(f"no {what} of kind {kind!r} is registered; known: {sorted(table)}")
+    return table[kind](spec, dtype, device)
+
+
+def build_mixer(spec, dtype, device) -> Mixer:
+    return _build(_MIXERS, "mixer", spec, dtype, device)
+
+
+def build_feed_forward(spec, dtype, device) -> FeedForward:
+    return _build(_FEED_FORWARDS, "feed-forward", spec, dtype, device)
+
+
+def build_norm(spec, dtype, device) -> Norm:
+    return _build(_NORMS, "norm", spec, dtype, device)
+
+
+def build_position(spec, dtype, device) -> PositionEncoding:
+    return _build(_POSITIONS, "position encoding", spec, dtype, device)
+
+
+def build_block(spec, dtype, device):
+    kind = getattr(spec, "arrangement", None)
+    if kind not in _ARRANGEMENTS:
+        raise ValueError(f"no block arrangement {kind!r} is registered; known: {sorted(_ARRANGEMENTS)}")
+    return _ARRANGEMENTS[kind](spec, dtype, device)

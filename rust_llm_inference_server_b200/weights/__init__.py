@@ -1,0 +1,3 @@
+from .loader import PlacedSource, WeightError, check_checkpoint
+from .random_init import random_tensor, random_tensors, write_random_model
+from .safetensors_io import Checkpoint, SafetensorsError, SafetensorsFile, open_model_dir, save_file
