@@ -1,0 +1,238 @@
+"""The engine loop: admits requests, lets the scheduler cut each step, runs the step function,
+samples, finishes and frees.
+
+Role of `Engine::{iterate, step}` and `Sequence::accept` (crates/engine/src/engine.rs:500-531,
+617-726, 404-429) without the thread, channels and text side: token ids in, token ids out.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import CacheStorage, host, plan_groups, size_groups
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .runner import ModelRunner, StepEntry
+
+
+class RequestError(ValueError):
+    """A request the engine refuses at intake (crates/engine/src/engine.rs:332-356)."""
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    prompt_token_ids: list
+    token_ids: list
+    finish_reason: str            # "stop" (end-of-sequence token) or "length" (max_tokens)
+    ttft: float                   # seconds from arrival to the first token
+    decode_time: float            # seconds from the first token to the last
+
+    @property
+    def decode_tokens_per_sec(self) -> float:
+        """(completion - 1) / decode_time (crates/engine/src/engine.rs:140-158)."""
+        n = len(self.token_ids)
+        return (n - 1) / self.decode_time if n > 1 and self.decode_time > 0 else 0.0
+
+
+@dataclass
+class _Sequence:
+    id: int
+    tokens: list
+    prompt_len: int
+    sampler: Sampler
+    max_tokens: int
+    ignore_eos: bool
+    arrived: float
+    first_token_at: float | None = None
+    finished: bool = False
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    generated_tokens: int = 0
+    step_tokens: int = 0
+    preemptions: int = 0
+    admitted_tokens: int = 0
+    prefix_hit_tokens: int = 0
+    running: int = 0
+    waiting: int = 0
+    kv_utilization: float = 0.0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+
+
+class LLMEngine:
+    def __init__(self, model, cfg: EngineConfig | None = None):
+        cfg = cfg or EngineConfig()
+        cfg.validate()
+        self.cfg = cfg
+        self.model = model
+        h = host()
+        groups = plan_groups(model.cache_slot_specs, cfg.block_size)
+        elem = torch.tensor([], dtype=model.dtype).element_size()
+        if cfg.num_blocks is not None:
+            for g in groups:
+                g.num_pages = int(cfg.num_blocks)
+        else:
+            size_groups(groups, cfg.kv_cache_bytes, elem)
+        if any(g.num_pages < 2 for g in groups):
+            raise ValueError(f"kv cache of {cfg.kv_cache_bytes} bytes holds fewer than 2 blocks")
+        self.groups = groups
+        max_batched = max(cfg.max_batched_tokens, cfg.max_num_seqs)   # engine.rs:265
+        sc = h.SchedulerConfig(cfg.max_num_seqs, max_batched, cfg.policy == "continuous", cfg.prefix_caching)
+        self.sched = h.Scheduler(sc, [h.GroupConfig(g.num_pages, g.page_size, g.window) for g in groups])
+        self.cache = self.sched.cache()
+        self.storage = CacheStorage(groups, model.call_state_specs, cfg.max_num_seqs, model.dtype, model.device)
+        # longest prompt plus completion: the option, the model's positions, and what the pool
+        # can hold with the watermark to spare (engine.rs:263-280)
+        self.max_seq_len = int(min(cfg.max_seq_len, model.spec.max_positions, self.cache.max_seq_tokens()))
+        self.runner = ModelRunner(model, self.cache, self.storage, self.max_seq_len)
+        self.eos_ids = set(model.spec.eos_token_ids)
+        self.seqs: dict[int, _Sequence] = {}
+        self._next_id = 0
+        self.stats = EngineStats()
+        self._params_host = torch.empty((cfg.max_num_seqs, 2), dtype=torch.int32, pin_memory=True)
+        self._params_dev = torch.empty((cfg.max_num_seqs, 2), dtype=torch.int32, device=model.device)
+        self._ids_dev = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
+        self._ids_host = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
+
+    # ---- intake ----
+
+    def add_request(self, prompt_token_ids, params: SamplingParams | None = None) -> int:
+        params = params or SamplingParams()
+        params.validate()
+        prompt = [int(t) for t in prompt_token_ids]
+        if not prompt:
+            raise RequestError("empty prompt or max_tokens of 0")
+        V = self.model.spec.vocab_size
+        if min(prompt) < 0 or max(prompt) >= V:
+            raise RequestError(f"prompt holds a token id outside the vocabulary of {V}")
+        total = len(prompt) + params.max_tokens
+        if total > self.max_seq_len:
+            raise RequestError(f"{total} tokens exceeds max_seq_len {self.max_seq_len}")
+        sid = self._next_id
+        self._next_id += 1
+        self.seqs[sid] = _Sequence(sid, prompt, len(prompt), Sampler(params), params.max_tokens,
+                                   params.ignore_eos, time.perf_counter())
+        self.sched.add(sid, prompt)
+        return sid
+
+    def cancel(self, request_id: int) -> None:
+        """Drops a request wherever it is and gives back what it holds (engine.rs:562-573)."""
+        if self.seqs.pop(request_id, None) is not None:
+            self.sched.remove(request_id)
+
+    def has_work(self) -> bool:
+        return self.sched.has_work()
+
+    # ---- one iteration ----
+
+    def step(self) -> list:
+        """Schedules, runs and samples one step; returns the requests that finished in it."""
+        seqs, preempted = self.sched.schedule()
+        self.stats.preemptions += len(preempted)
+        if not seqs:
+            if self.sched.has_work():
+                # no progress is possible: fail everything rather than spin (engine.rs:516-522)
+                ids = list(self.seqs)
+                for sid in ids:
+                    self.cancel(sid)
+                raise RuntimeError(f"scheduler made no progress with {len(ids)} requests pending")
+            return []
+        entries = []
+        sample_rows = []            # (sequence, row among the wanted rows)
+        for sid, start, end in seqs:
+            s = self.seqs[sid]
+            caught_up = end == len(s.tokens)
+            entries.append(StepEntry(sid, s.tokens[start:end], start, [end - start - 1] if caught_up else []))
+            if caught_up:
+                sample_rows.append(s)
+        st = self.runner.prepare(entries)
+        logits = self.runner.forward(st)
+        self.stats.h2d_bytes += st.h2d_bytes
+        self.stats.steps += 1
+        self.stats.step_tokens += st.n_tokens
+        for sid, start, end in seqs:
+            self.sched.advance(sid, end)
+        finished = []
+        if sample_rows:
+            tokens = self._sample(logits, sample_rows)
+            now = time.perf_counter()
+            for s, tok in zip(sample_rows, tokens):
+                out = self._accept(s, int(tok), now)
+                if out is not None:
+                    finished.append(out)
+        self._publish()
+        return finished
+
+    def _sample(self, logits: torch.Tensor, rows: list) -> list:
+        n = len(rows)
+        modes = [s.sampler.device_mode(len(s.tokens)) for s in rows]
+        out = [0] * n
+        dev_idx = [i for i, m in enumerate(modes) if m is not None]
+        if dev_idx:
+            ph = self._params_host.numpy().view(np.uint32)
+            for i in range(n):
+                ph[i] = modes[i] if modes[i] is not None else (0, 0)
+            self._params_dev[:n].copy_(self._params_host[:n], non_blocking=True)
+            ids = ops.sample_rows(logits, self._params_dev[:n], self._ids_dev[:n])
+            self._ids_host[:n].copy_(ids, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            got = self._ids_host[:n].tolist()
+            self.stats.h2d_bytes += n * 8
+            self.stats.d2h_bytes += n * 4
+            for i in dev_idx:
+                out[i] = got[i]
+        host_idx = [i for i, m in enumerate(modes) if m is None]
+        if host_idx:
+            sel = torch.tensor(host_idx, device=logits.device)
+            rows_host = logits.index_select(0, sel).to("cpu").numpy()
+            self.stats.d2h_bytes += rows_host.nbytes
+            for j, i in enumerate(host_idx):
+                s = rows[i]
+                out[i] = s.sampler.sample_host(rows_host[j], s.tokens, len(s.tokens))
+        return out
+
+    def _accept(self, s: _Sequence, token: int, now: float):
+        """Records a sampled token; finishes the request on end-of-sequence (not appended) unless
+        `ignore_eos`, or at `max_tokens` (engine.rs:404-429)."""
+        if s.first_token_at is None:
+            s.first_token_at = now
+        if token in self.eos_ids and not s.ignore_eos:
+            return self._finish(s, "stop", now)
+        s.tokens.append(token)
+        self.stats.generated_tokens += 1
+        if len(s.tokens) - s.prompt_len >= s.max_tokens:
+            return self._finish(s, "length", now)
+        self.sched.append_token(s.id, token)
+        return None
+
+    def _finish(self, s: _Sequence, reason: str, now: float) -> RequestOutput:
+        s.finished = True
+        self.sched.remove(s.id)
+        del self.seqs[s.id]
+        first = s.first_token_at if s.first_token_at is not None else now
+        return RequestOutput(s.id, s.tokens[:s.prompt_len], s.tokens[s.prompt_len:], reason,
+                             first - s.arrived, now - first)
+
+    def _publish(self) -> None:
+        st = self.stats
+        st.running = self.sched.num_running()
+        st.waiting = self.sched.num_waiting()
+        st.kv_utilization = self.cache.utilization()
+        st.admitted_tokens = self.sched.admitted_tokens()
+        st.prefix_hit_tokens = self.sched.cached_tokens()
+
+    def run_to_completion(self) -> list:
+        done = []
+        while self.has_work():
+            done.extend(self.step())
+        return done
