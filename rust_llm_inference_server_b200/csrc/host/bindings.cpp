@@ -121,6 +121,7 @@ PYBIND11_MODULE(_rlis_host, m) {
         })
         .def("fits", &CacheManager::fits)
         .def("watermark", &CacheManager::watermark)
+        .def("set_watermark", &CacheManager::set_watermark)
         .def("max_seq_tokens", &CacheManager::max_seq_tokens)
         .def("adopt_prefix", &CacheManager::adopt_prefix)
         .def("register_page", &CacheManager::register_page)
@@ -138,11 +139,12 @@ PYBIND11_MODULE(_rlis_host, m) {
              py::arg("cu_seqlens").noconvert(), py::arg("state_slots").noconvert());
 
     py::class_<SchedulerConfig>(m, "SchedulerConfig")
-        .def(py::init([](int max_num_seqs, int max_batched_tokens, bool continuous, bool prefix_caching) {
+        .def(py::init([](int max_num_seqs, int max_batched_tokens, bool continuous, bool prefix_caching, int watermark_blocks) {
                  SchedulerConfig c; c.max_num_seqs = max_num_seqs; c.max_batched_tokens = max_batched_tokens;
-                 c.continuous = continuous; c.prefix_caching = prefix_caching; return c;
+                 c.continuous = continuous; c.prefix_caching = prefix_caching; c.watermark_blocks = watermark_blocks; return c;
              }), py::arg("max_num_seqs") = 64, py::arg("max_batched_tokens") = 2048,
-             py::arg("continuous") = true, py::arg("prefix_caching") = true)
+             py::arg("continuous") = true, py::arg("prefix_caching") = true, py::arg("watermark_blocks") = -1)
+        .def_readwrite("watermark_blocks", &SchedulerConfig::watermark_blocks)
         .def_readwrite("max_num_seqs", &SchedulerConfig::max_num_seqs)
         .def_readwrite("max_batched_tokens", &SchedulerConfig::max_batched_tokens)
         .def_readwrite("continuous", &SchedulerConfig::continuous)

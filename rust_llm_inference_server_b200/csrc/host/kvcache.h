@@ -360,7 +360,9 @@ public:
 
     // Pages kept free at admission so that running requests can grow
     // (crates/engine/src/engine.rs:268: max(1, pages / 100)).
-    int watermark(int g) const { return std::max(1, groups_[g].num_pages / 100); }
+    int watermark(int g) const { return watermark_ >= 0 ? watermark_ : std::max(1, groups_[g].num_pages / 100); }
+    // A fixed number of pages instead of the default rule; negative restores the rule.
+    void set_watermark(int pages) { watermark_ = pages; }
 
     // Longest request that can ever be admitted.
     size_t max_seq_tokens() const {
@@ -450,6 +452,7 @@ private:
     std::vector<int> free_slots_;
     std::unordered_map<SeqId, int> slot_of_;
     int num_state_slots_ = 0;
+    int watermark_ = -1;
 };
 
 }  // namespace rlis

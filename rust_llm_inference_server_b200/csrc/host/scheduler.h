@@ -28,6 +28,7 @@ struct SchedulerConfig {
     int max_batched_tokens = 2048;
     bool continuous = true;       // false: static batching
     bool prefix_caching = true;
+    int watermark_blocks = -1;    // pages kept free at admission; negative: max(1, pages / 100)
 };
 
 struct ScheduledSeq {
@@ -52,6 +53,7 @@ public:
         if (cfg_.max_batched_tokens < cfg_.max_num_seqs)
             throw std::invalid_argument("max_batched_tokens must cover one decode token per sequence");
         if (cfg_.prefix_caching && !cache_.prefix_reuse_possible()) cfg_.prefix_caching = false;
+        cache_.set_watermark(cfg_.watermark_blocks);
     }
 
     CacheManager& cache() { return cache_; }

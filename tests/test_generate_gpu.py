@@ -1,0 +1,139 @@
+"""Generation through the Python entry point on the GPU: greedy tokens equal the plain
+implementation's; batching, portions, preemption and prefix reuse change nothing; sampling is
+reproducible and does not depend on the batch."""
+
+import numpy as np
+import pytest
+
+from tests.plain import llama_plain as P
+from tests.tiny_configs import CONFIGS, load_plain_weights, make_model_dir
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(which, lens, seed=1):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, CONFIGS[which]["vocab_size"], size=n).tolist() for n in lens]
+
+
+def make_llm(model_root, which, dtype, **kw):
+    from rust_llm_inference_server_b200 import LLM
+    opts = dict(max_seq_len=128, num_blocks=64, block_size=8, max_num_seqs=4, max_batched_tokens=2048)
+    opts.update(kw)
+    return LLM(make_model_dir(model_root, which), dtype=dtype, **opts)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_equals_the_plain_implementation(model_root, dtype):
+    """Tiny configuration A of the workload: prompts of 1, 7, 13 and 32 tokens, 16 greedy tokens."""
+    from rust_llm_inference_server_b200 import SamplingParams
+    w = load_plain_weights(make_model_dir(model_root, "A"))
+    prompts = prompts_for("A", [1, 7, 13, 32])
+    llm = make_llm(model_root, "A", dtype)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=16))
+    for p, o in zip(prompts, outs):
+        want = P.greedy_generate(w, CONFIGS["A"], p, 16)
+        if dtype == "float32":
+            assert o.token_ids == want
+        else:
+            # a flip is tolerated only at a near tie of the float32 logits
+            # (the reference's rule, crates/model/tests/parity.rs:30-35)
+            for i, (a, b) in enumerate(zip(o.token_ids, want)):
+                if a != b:
+                    lg = np.sort(P.forward_logits(w, CONFIGS["A"], p + want[:i])[-1].numpy())
+                    assert lg[-1] - lg[-2] < 0.02
+                    break
+        assert o.finish_reason == "length" and len(o.token_ids) == 16 and o.prompt_token_ids == p
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batching_portions_preemption_and_prefix_reuse_change_nothing(model_root, dtype):
+    from rust_llm_inference_server_b200 import SamplingParams
+    which = "B"
+    shared = prompts_for(which, [48], seed=5)[0]
+    prompts = prompts_for(which, [3, 60, 21, 90]) + [shared + [7, 8, 9], shared + [11] * 20]
+    sp = SamplingParams(max_tokens=24)
+    base = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=64, block_size=16, max_num_seqs=1,
+                    prefix_caching=False)
+    solo = [base.generate([p], sp)[0].token_ids for p in prompts]
+
+    batched = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=64, block_size=16, max_num_seqs=6,
+                       prefix_caching=False)
+    assert [o.token_ids for o in batched.generate(prompts, sp)] == solo
+
+    cut = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=64, block_size=16, max_num_seqs=4,
+                   max_batched_tokens=16, prefix_caching=False)
+    assert [o.token_ids for o in cut.generate(prompts, sp)] == solo
+
+    tight = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=12, block_size=16, max_num_seqs=6,
+                     prefix_caching=True)
+    assert [o.token_ids for o in tight.generate(prompts, sp)] == solo
+    assert tight.engine.stats.preemptions > 0
+    assert tight.engine.sched.check() == "" and tight.engine.cache.num_free_pages(0) == 12
+
+    for seats in (1, 2):
+        pc = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=64, block_size=16,
+                      max_num_seqs=seats, prefix_caching=True)
+        assert [o.token_ids for o in pc.generate(prompts, sp)] == solo
+        if seats == 1:   # one after the other: the second holder of the prefix finds its three full pages
+            assert pc.engine.stats.prefix_hit_tokens >= 48
+        assert [o.token_ids for o in pc.generate(prompts, sp)] == solo      # now everything is cached
+        full_pages = sum((len(p) - 1) // 16 * 16 for p in prompts)   # never the page of the last token
+        assert pc.engine.stats.prefix_hit_tokens >= full_pages + (48 if seats == 1 else 0)
+
+    static = make_llm(model_root, which, dtype, max_seq_len=256, num_blocks=64, block_size=16, max_num_seqs=3,
+                      scheduler="static")
+    assert [o.token_ids for o in static.generate(prompts, sp)] == solo
+
+
+def test_seeded_sampling_is_reproducible_and_ignores_neighbours(model_root):
+    from rust_llm_inference_server_b200 import SamplingParams
+    which = "B"
+    prompts = prompts_for(which, [5, 40, 17, 9])
+    llm = make_llm(model_root, which, "float32", max_seq_len=256, block_size=16)
+    w = load_plain_weights(make_model_dir(model_root, which))
+    for sp in (SamplingParams(max_tokens=12, temperature=0.8, seed=3),
+               SamplingParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=3),
+               SamplingParams(max_tokens=12, temperature=1.1, top_k=20, repetition_penalty=1.2, seed=3)):
+        a = [o.token_ids for o in llm.generate(prompts, sp)]
+        b = [llm.generate([p], sp)[0].token_ids for p in prompts]
+        assert a == b
+        sp2 = SamplingParams(**{**sp.__dict__, "seed": 4})
+        assert [o.token_ids for o in llm.generate(prompts, sp2)] != a
+    # temperature-only rows are drawn on the device with the reference's noise: replay with the plain sampler
+    sp = SamplingParams(max_tokens=6, temperature=0.8, seed=3)
+    got = llm.generate([prompts[0]], sp)[0].token_ids
+    toks = list(prompts[0])
+    for t in got:
+        lg = P.forward_logits(w, CONFIGS[which], toks)[-1].numpy()
+        assert P.sample_row(lg, 0.8, P.row_key(3, len(toks))) == t
+        toks.append(t)
+
+
+def test_end_of_sequence_and_limits(model_root, tmp_path):
+    import json, os, shutil
+    from rust_llm_inference_server_b200 import LLM, SamplingParams
+    from rust_llm_inference_server_b200.engine.engine import RequestError
+    src = make_model_dir(model_root, "A")
+    w = load_plain_weights(src)
+    p = prompts_for("A", [9])[0]
+    want = P.greedy_generate(w, CONFIGS["A"], p, 10)
+    eos = want[4]
+    d = str(tmp_path / "with_eos")
+    shutil.copytree(src, d)
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    cfg["eos_token_id"] = eos
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    llm = LLM(d, dtype="float32", max_seq_len=64, num_blocks=16, block_size=8, max_num_seqs=2)
+    o = llm.generate([p], SamplingParams(max_tokens=10))[0]
+    first = want.index(eos)
+    assert o.finish_reason == "stop" and o.token_ids == want[:first]     # the end token is not appended
+    o = llm.generate([p], SamplingParams(max_tokens=10, ignore_eos=True))[0]
+    assert o.finish_reason == "length" and o.token_ids == want
+    with pytest.raises(RequestError, match="exceeds max_seq_len"):
+        llm.generate([p], SamplingParams(max_tokens=60))
+    with pytest.raises(RequestError):
+        llm.generate([[]], SamplingParams())
+    with pytest.raises(RequestError, match="vocabulary"):
+        llm.generate([[1, 999]], SamplingParams())
+    assert llm.engine.cache.num_free_pages(0) == 16
