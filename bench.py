@@ -1,0 +1,308 @@
+#!/usr/bin/env python3
+"""Benchmark of the decode step (and a 2,048-token prefill) at the Llama-3.2-1B layer sizes with
+random bfloat16 weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens a second over K device-timed decode steps of a
+batch of 8 requests whose context ends at 4,096 tokens (teacher-forced random tokens, sampler
+kernel included, CUDA events around the K steps).  `e2e` is the same quantity through the Python
+entry point (`LLM.stream`): every step uploads its inputs from pinned host memory and reads its
+sampled token ids back.  Method after the reference's own micro-benchmarks (warm-up, then a timed
+loop with a device synchronisation on both sides, crates/model/examples/decode_profile.rs:47-62).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# configs[2] of the baseline description: Llama-3.2-1B sizes
+CONFIG_1B = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+SEED = 4
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines: list = []
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return
+        idx = os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0] or "0"
+        try:
+            self.proc = subprocess.Popen(
+                [exe, "-i", idx, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def weight_bytes(cfg: dict, n_layers: int, elem: int = 2) -> int:
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nh, nkv, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    per_layer = ((nh + 2 * nkv) * d * H + H * nh * d + 3 * I * H) * elem + 2 * H * 4
+    return n_layers * per_layer + V * H * elem + H * 4      # LM head (tied table) read once
+
+
+def kv_bytes_per_token(cfg: dict, n_layers: int, elem: int = 2) -> int:
+    return 2 * n_layers * cfg["num_key_value_heads"] * cfg["head_dim"] * elem
+
+
+def prefill_flops(cfg: dict, n_layers: int, T: int) -> float:
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nh, nkv, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    proj = 2.0 * T * ((nh + 2 * nkv) * d * H + H * nh * d + 3 * I * H)
+    attn = 2.0 * T * T * nh * d          # causal: QK^T and PV over half the square
+    return n_layers * (proj + attn) + 2.0 * V * H
+
+
+def run_reference(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is a Rust workspace on the candle library (Metal kernels); pip finds "
+                       "neither setup.py nor pyproject.toml and there is no cargo/rustc here, so it cannot be installed",
+    }))
+    return 0
+
+
+def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch):
+    """Device-timed decode: B requests, each step one teacher-forced token per request and the
+    sampler kernel; the last step's context is `ctx_end`.  Returns (ms per step, launches per step)."""
+    import numpy as np
+    from rust_llm_inference_server_b200 import ops
+    from rust_llm_inference_server_b200.engine import StepEntry
+
+    eng = llm.engine
+    runner, cache = eng.runner, eng.cache
+    V = llm.model.spec.vocab_size
+    rng = np.random.default_rng(B)
+    total = warmup + steps
+    ctx0 = ctx_end - total
+    ids = list(range(10_000, 10_000 + B))
+    for sid in ids:
+        assert cache.acquire_state_slot(sid) >= 0
+        assert cache.reserve(sid, ctx_end), "cache pool too small for the benchmark"
+    # fill the cache up to ctx0 with a prompt cut into portions of at most 2,048 tokens
+    for sid in ids:
+        pos = 0
+        while pos < ctx0:
+            n = min(2048, ctx0 - pos)
+            runner.step([StepEntry(sid, rng.integers(0, V, size=n).tolist(), pos, [])])
+            pos += n
+    params = torch.zeros((B, 2), dtype=torch.int32, device=llm.model.device)     # greedy rows
+    out_ids = torch.empty((B,), dtype=torch.int32, device=llm.model.device)
+    toks = rng.integers(0, V, size=(total, B))
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    launches = 0
+    for i in range(total):
+        if i == warmup:
+            torch.cuda.synchronize()
+            l0 = runner.launches
+            start.record()
+        logits = runner.step([StepEntry(sid, [int(toks[i, b])], ctx0 + i, [0]) for b, sid in enumerate(ids)])
+        runner.sample(logits, params, out_ids)
+    end.record()
+    torch.cuda.synchronize()
+    launches = runner.launches - l0
+    ms = start.elapsed_time(end) / steps
+    for sid in ids:
+        cache.free(sid)
+    return ms, launches / steps
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+
+    from rust_llm_inference_server_b200 import LLM, SamplingParams
+
+    pk, pk_src = peaks()
+    cfg = dict(CONFIG_1B)
+    n_layers_full = cfg["num_hidden_layers"]
+    n_layers = args.layers or n_layers_full
+    cfg["num_hidden_layers"] = n_layers
+    B = args.batch
+    total = args.warmup + args.steps
+    page = 16
+    max_b = max(B, 64)
+    pool_tokens = max_b * (CONTEXT + page)
+    llm = LLM.from_random(cfg, SEED, dtype="bfloat16", on_device=True, max_seq_len=CONTEXT + page,
+                          num_blocks=pool_tokens // page + 64, block_size=page, max_num_seqs=max_b,
+                          max_batched_tokens=max(2048, max_b), prefix_caching=False)
+    runner = llm.engine.runner
+
+    # ---- prefill of one 2,048-token prompt ----
+    from rust_llm_inference_server_b200.engine import StepEntry
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    cache = llm.engine.cache
+    pre_ms = []
+    for it in range(5):
+        sid = 500 + it
+        cache.acquire_state_slot(sid)
+        assert cache.reserve(sid, PREFILL_TOKENS)
+        toks = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        runner.step([StepEntry(sid, toks, 0, [PREFILL_TOKENS - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        pre_ms.append(s.elapsed_time(e))
+        cache.free(sid)
+    prefill_ms = statistics.median(pre_ms[2:])
+    pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(pf / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode points at batch 1 and 64, then the headline batch under the clock sampler ----
+    points = {}
+    for b in (1, 64):
+        ms, _ = decode_run(llm, b, max(16, args.steps // 2), args.warmup, CONTEXT, torch)
+        points[f"decode_b{b}"] = round(b / (ms / 1e3), 1)
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = decode_run(llm, B, args.steps, args.warmup, CONTEXT, torch)
+    clk = clocks.stop()
+    value = B / (ms / 1e3)
+    mean_ctx = CONTEXT - args.steps / 2
+    step_bytes = weight_bytes(cfg, n_layers) + B * mean_ctx * kv_bytes_per_token(cfg, n_layers)
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
+
+    # ---- end to end through the Python entry point ----
+    prompts = [rng.integers(0, V, size=CONTEXT - total - 1).tolist() for _ in range(B)]
+    sp = SamplingParams(max_tokens=total + 1, ignore_eos=True)
+    eng = llm.engine
+    h2d0 = d2h0 = 0
+    t0 = t1 = None
+    n_decode = 0
+    for ev in llm.stream(prompts, sp):
+        if not ev.all_decoding:
+            continue
+        n_decode += 1
+        if n_decode == args.warmup:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            h2d0, d2h0 = eng.stats.h2d_bytes, eng.stats.d2h_bytes
+        elif n_decode == args.warmup + args.steps:
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            h2d1, d2h1 = eng.stats.h2d_bytes, eng.stats.d2h_bytes
+    e2e_ms = (t1 - t0) * 1e3 / args.steps
+    e2e = {"value": round(B / (e2e_ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": (h2d1 - h2d0) // args.steps, "d2h_bytes_per_step": (d2h1 - d2h0) // args.steps}
+
+    line = {
+        "metric": "decode tokens/s, batch 8, context 4096 (Llama-3.2-1B sizes, random bf16 weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random-init weights N(0,0.02) seed 4",
+        "impl": "ours",
+        "config": {
+            "model": "llama-3.2-1b-sizes", "layers": n_layers, "layers_in_config": n_layers_full,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": V,
+            "tied": True, "rope": "theta 5e5 llama3 32/1/4/8192", "eps": 1e-5,
+            "global_batch": B, "seq_len": CONTEXT, "page_size": page, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (weights 2.47 GB per step)", "kv_dtype": "bf16",
+        },
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": int(round(launches * args.steps)), "clocks": clk,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -55,6 +55,17 @@ class _Sequence:
 
 
 @dataclass
+class StepEvent:
+    """What one engine step did (the stream the reference sends as `Event`s,
+    crates/engine/src/engine.rs:115-120, without the text)."""
+    n_tokens: int
+    n_seqs: int
+    all_decoding: bool            # every scheduled request ran exactly one token
+    new_tokens: dict              # request id -> token sampled in this step
+    finished: list                # RequestOutput of the requests that ended in this step
+
+
+@dataclass
 class EngineStats:
     steps: int = 0
     generated_tokens: int = 0
@@ -140,6 +151,7 @@ class LLMEngine:
         seqs, preempted = self.sched.schedule()
         self.stats.preemptions += len(preempted)
         if not seqs:
+            self.last_step = StepEvent(0, 0, False, {}, [])
             if self.sched.has_work():
                 # no progress is possible: fail everything rather than spin (engine.rs:516-522)
                 ids = list(self.seqs)
@@ -163,14 +175,17 @@ class LLMEngine:
         for sid, start, end in seqs:
             self.sched.advance(sid, end)
         finished = []
+        new_tokens = {}
         if sample_rows:
             tokens = self._sample(logits, sample_rows)
             now = time.perf_counter()
             for s, tok in zip(sample_rows, tokens):
+                new_tokens[s.id] = int(tok)
                 out = self._accept(s, int(tok), now)
                 if out is not None:
                     finished.append(out)
         self._publish()
+        self.last_step = StepEvent(st.n_tokens, st.n_seqs, st.all_decode, new_tokens, finished)
         return finished
 
     def _sample(self, logits: torch.Tensor, rows: list) -> list:

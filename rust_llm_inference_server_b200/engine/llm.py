@@ -14,7 +14,7 @@ from ..config.engine_config import EngineConfig
 from ..config.model_config import read_config_json
 from ..models import build_model, load_model
 from ..sampling.params import SamplingParams
-from ..weights.random_init import random_tensors
+from ..weights.random_init import random_tensors, random_tensors_on_device
 from ..weights.safetensors_io import Checkpoint
 from .engine import LLMEngine, RequestOutput
 
@@ -36,16 +36,17 @@ class LLM:
 
     @classmethod
     def from_random(cls, config_json: dict, seed: int, dtype: str = "bfloat16", device: str = "cuda",
-                    **engine_options) -> "LLM":
-        """Random-weights mode without a folder: the same tensors `write_random_model` would store."""
+                    on_device: bool = False, **engine_options) -> "LLM":
+        """Random-weights mode without a folder: the same tensors `write_random_model` would store
+        (or, with `on_device`, tensors of the same distributions drawn by the GPU's generator)."""
         model = build_model(config_json, dtype, device)
         store = "bfloat16" if model.dtype == torch.bfloat16 else "float32"
-        model.load(Checkpoint(tensors=random_tensors(config_json, seed, store)))
+        make = (lambda: random_tensors_on_device(config_json, seed, device, store)) if on_device \
+            else (lambda: random_tensors(config_json, seed, store))
+        model.load(Checkpoint(tensors=make()))
         return cls(None, dtype=dtype, device=device, _model=model, **engine_options)
 
-    def generate(self, prompt_token_ids, sampling_params=None) -> list:
-        """`prompt_token_ids`: a list of token-id lists.  `sampling_params`: one SamplingParams for
-        all, or a list.  Returns one RequestOutput per prompt, in the order of the prompts."""
+    def _submit(self, prompt_token_ids, sampling_params):
         if prompt_token_ids and isinstance(prompt_token_ids[0], int):
             prompt_token_ids = [prompt_token_ids]
         n = len(prompt_token_ids)
@@ -54,6 +55,19 @@ class LLM:
         plist = sampling_params if isinstance(sampling_params, (list, tuple)) else [sampling_params] * n
         if len(plist) != n:
             raise ValueError(f"{n} prompts but {len(plist)} sampling parameter sets")
-        ids = [self.engine.add_request(p, sp) for p, sp in zip(prompt_token_ids, plist)]
+        return [self.engine.add_request(p, sp) for p, sp in zip(prompt_token_ids, plist)]
+
+    def stream(self, prompt_token_ids, sampling_params=None):
+        """Like `generate`, but yields a StepEvent after every engine step (tokens as they are
+        sampled, requests as they finish), as the reference streams events to its caller."""
+        self._submit(prompt_token_ids, sampling_params)
+        while self.engine.has_work():
+            self.engine.step()
+            yield self.engine.last_step
+
+    def generate(self, prompt_token_ids, sampling_params=None) -> list:
+        """`prompt_token_ids`: a list of token-id lists.  `sampling_params`: one SamplingParams for
+        all, or a list.  Returns one RequestOutput per prompt, in the order of the prompts."""
+        ids = self._submit(prompt_token_ids, sampling_params)
         done = {o.request_id: o for o in self.engine.run_to_completion()}
         return [done[i] for i in ids]

@@ -72,6 +72,7 @@ class ModelRunner:
         self._meta_dev = None
         self._graph_keepalive: list = []
         self._upload_done = None
+        self._graph_launches = 0
 
     # ---- scratch memory that keeps its address while it is large enough ----
 
@@ -196,3 +197,12 @@ class ModelRunner:
 
     def step(self, entries: list):
         return self.forward(self.prepare(entries))
+
+    def sample(self, logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None):
+        """One token id per row of logits on the device (greedy or Gumbel-max; see ops.sample_rows)."""
+        return ops.sample_rows(logits, params, out)
+
+    @property
+    def launches(self) -> int:
+        """Launches of this package's kernels so far (a graph replay counts the launches it holds)."""
+        return ops.launch_count + self._graph_launches

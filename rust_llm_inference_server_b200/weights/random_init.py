@@ -45,6 +45,22 @@ def random_tensors(config_json: dict, seed: int, store_dtype: str = "bfloat16") 
     return {name: random_tensor(seed, name, shape, kind).to(dt) for name, (shape, kind) in kinds.items()}
 
 
+def random_tensors_on_device(config_json: dict, seed: int, device, store_dtype: str = "bfloat16") -> dict:
+    """The same distributions drawn by the device's generator (other values than
+    `random_tensors`): fast enough for benchmark-sized models."""
+    arch = lookup_architecture(config_json)
+    kinds = arch.tensor_kinds(arch.parse_config(config_json))
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    out = {}
+    for name, (shape, kind) in kinds.items():
+        x = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32) * 0.02
+        if kind == "norm":
+            x += 1.0
+        out[name] = x.to(_STORE[store_dtype])
+    return out
+
+
 def write_random_model(config_json: dict, out_dir: str, seed: int, store_dtype: str = "bfloat16") -> str:
     """Creates `out_dir` with config.json and model.safetensors; returns out_dir."""
     os.makedirs(out_dir, exist_ok=True)
