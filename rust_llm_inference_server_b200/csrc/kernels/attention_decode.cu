@@ -1,0 +1,264 @@
+// Decode attention over the paged cache, split over the context: one query token per request,
+// grid (kv head, request, split).  All query heads of a GQA group share every K and V row that the
+// CTA reads, so the cache is streamed from HBM once per kv head.
+//
+// Role in the reference: the Metal kernels paged_attention_decode{,_split} and
+// paged_attention_reduce (crates/model/src/paged_attention.metal:56-304) and their split plan
+// (crates/model/src/paged_attention.rs:21-36): lanes take one key position each for q.k, an online
+// softmax per block of positions, then lanes take slices of the head dimension for p.v; partial
+// (m, l, acc) per split, merged afterwards.  Scores, softmax and p.v are float32; q.k accumulates
+// over d in index order.
+//
+// Layout here: a warp owns blocks of 32 keys (strided over the CTA's 4 warps) and keeps its own
+// running (m, l, acc); the four warps are merged through shared memory at the end, so the main
+// loop has no block-wide barrier.  p.v: 8-element (16-byte) slices of a V row per lane.
+//
+// Scratch: when splits > 1 the kernel writes partial results [request, head, split, d + 2] float32
+// to a caller-provided buffer and `attention_decode_combine` merges them.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+
+// NREP = query heads per kv head, D8 = head_dim / 8 (16-byte chunks per row).
+template <int NREP>
+__global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
+    const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
+    const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int d, int page_size,
+    float scale, int window, int splits) {
+    extern __shared__ __align__(16) float smem[];
+    // smem: q [NREP][d] | p per warp [DEC_WARPS][32][NREP] | merge area
+    float* qs = smem;
+    float* ps = qs + NREP * d;
+    float* merge = ps + DEC_WARPS * 32 * NREP;   // [DEC_WARPS][groups][NREP][d] then [DEC_WARPS][NREP][2]
+
+    const int kvh = blockIdx.x, bi = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = dec_rows[bi];
+    const int seq = dec_seqs[bi];
+    const int ctx = ctx_lens[seq];          // keys 0 .. ctx-1; the query sits at ctx-1
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const int d8 = d >> 3;
+
+    // this split's range of keys, in whole blocks of 32
+    const int lo_all = window > 0 ? max(0, ctx - window) : 0;
+    const int first_blk = lo_all >> 5;
+    const int n_blk = ((ctx + 31) >> 5) - first_blk;
+    const int blk_per_split = (n_blk + splits - 1) / splits;
+    const int blk0 = first_blk + split * blk_per_split;
+    const int blk1 = min(blk0 + blk_per_split, first_blk + n_blk);
+
+    for (int i = threadIdx.x; i < NREP * d; i += DEC_THREADS) {
+        const int h = i / d, j = i - h * d;
+        qs[i] = to_f<bf16>(q[((size_t)row * nh + kvh * NREP + h) * d + j]);
+    }
+    __syncthreads();
+
+    float m[NREP], l[NREP];
+    float acc[NREP][8];
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        m[h] = -INFINITY;
+        l[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+    }
+    // p.v mapping: lane -> (key within a group, 16-byte chunk of the row)
+    const int kpi = 32 / d8 > 0 ? 32 / d8 : 1;          // keys per iteration of a warp (d8 <= 32)
+    const int pv_key = lane / d8, pv_chunk = lane - pv_key * d8;
+    const bool pv_active = lane < kpi * d8;
+    float* pw = ps + warp * 32 * NREP;
+
+    for (int blk = blk0 + warp; blk < blk1; blk += DEC_WARPS) {
+        const int key = (blk << 5) + lane;
+        const bool valid = key >= lo_all && key < ctx;
+        float s[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) s[h] = -INFINITY;
+        if (valid) {
+            const int page = table[key / page_size];
+            const bf16* krow = k_cache + (((size_t)page * nkv + kvh) * page_size + key % page_size) * d;
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) s[h] = 0.f;
+            for (int c = 0; c < d8; ++c) {
+                float kf[8];
+                load16<bf16>(krow + c * 8, kf);
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) {
+                    const float4 qa = *reinterpret_cast<const float4*>(qs + h * d + c * 8);
+                    const float4 qb = *reinterpret_cast<const float4*>(qs + h * d + c * 8 + 4);
+                    float t = s[h];
+                    t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t);
+                    t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
+                    t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t);
+                    t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
+                    s[h] = t;
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) s[h] *= scale;
+        }
+        float corr[NREP];
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            const float m_new = fmaxf(m[h], warp_max(s[h]));   // finite: every block has a valid key
+            const float p = valid ? expf(s[h] - m_new) : 0.f;
+            corr[h] = expf(m[h] - m_new);
+            l[h] = l[h] * corr[h] + warp_sum(p);
+            m[h] = m_new;
+            pw[lane * NREP + h] = p;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < NREP; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] *= corr[h];
+        if (pv_active) {
+            for (int k0 = 0; k0 < 32; k0 += kpi) {
+                const int kk = k0 + pv_key;
+                const int kidx = (blk << 5) + kk;
+                if (kk < 32 && kidx >= lo_all && kidx < ctx) {
+                    const int page = table[kidx / page_size];
+                    const bf16* vrow = v_cache + (((size_t)page * nkv + kvh) * page_size + kidx % page_size) * d;
+                    float vf[8];
+                    load16<bf16>(vrow + pv_chunk * 8, vf);
+#pragma unroll
+                    for (int h = 0; h < NREP; ++h) {
+                        const float p = pw[kk * NREP + h];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // Per-warp results to shared memory.  Lanes with the same chunk but another key group hold
+    // partial sums over different keys: each group writes its own copy, summed below in a fixed
+    // order.  stage[warp][group][h][d]; ml[warp][h][2].
+    const int groups = kpi;
+    float* stage = merge + (size_t)warp * groups * NREP * d;
+    if (pv_active) {
+#pragma unroll
+        for (int h = 0; h < NREP; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) stage[((size_t)pv_key * NREP + h) * d + pv_chunk * 8 + e] = acc[h][e];
+    }
+    float* ml = merge + (size_t)DEC_WARPS * groups * NREP * d;
+    if (lane == 0) {
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            ml[(warp * NREP + h) * 2] = m[h];
+            ml[(warp * NREP + h) * 2 + 1] = l[h];
+        }
+    }
+    __syncthreads();
+
+    // merge the warps: big = max m; out = sum acc_w * exp(m_w - big) / sum l_w * exp(m_w - big)
+    for (int i = threadIdx.x; i < NREP * d; i += DEC_THREADS) {
+        const int h = i / d, j = i - h * d;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) big = fmaxf(big, ml[(w * NREP + h) * 2]);
+        float a = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = ml[(w * NREP + h) * 2];
+            if (mw == -INFINITY) continue;          // this warp had no block of keys
+            const float wgt = expf(mw - big);
+            float aw = 0.f;
+            for (int g = 0; g < groups; ++g) aw += merge[(((size_t)w * groups + g) * NREP + h) * d + j];
+            a += aw * wgt;
+            lsum += ml[(w * NREP + h) * 2 + 1] * wgt;
+        }
+        const int head = kvh * NREP + h;
+        if (splits == 1) {
+            out[((size_t)row * nh + head) * d + j] = from_f<bf16>(a / lsum);
+        } else {
+            float* pr = partial + (((size_t)bi * nh + head) * splits + split) * (d + 2);
+            pr[j] = a;
+            if (j == 0) {
+                pr[d] = big;
+                pr[d + 1] = lsum;
+            }
+        }
+    }
+}
+
+// Merges the splits: big = max m over non-empty splits, w = exp(m - big),
+// out = sum acc * w / sum l * w (crates/model/src/paged_attention.metal:276-304).
+__global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                           const int* __restrict__ dec_rows, int nh, int d,
+                                           int splits) {
+    const int bi = blockIdx.y, head = blockIdx.x;
+    const float* pr = partial + ((size_t)bi * nh + head) * splits * (d + 2);
+    float big = -INFINITY;
+    for (int s = 0; s < splits; ++s) big = fmaxf(big, pr[(size_t)s * (d + 2) + d]);
+    const int row = dec_rows[bi];
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float a = 0.f, lsum = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* r = pr + (size_t)s * (d + 2);
+            const float w = r[d] == -INFINITY ? 0.f : expf(r[d] - big);
+            a += r[j] * w;
+            lsum += r[d + 1] * w;
+        }
+        out[((size_t)row * nh + head) * d + j] = from_f<bf16>(a / lsum);
+    }
+}
+
+size_t decode_smem_bytes(int nrep, int d) {
+    const int groups = 32 / (d / 8);
+    return sizeof(float) * ((size_t)nrep * d + DEC_WARPS * 32 * nrep + (size_t)DEC_WARPS * groups * nrep * d +
+                            (size_t)DEC_WARPS * nrep * 2);
+}
+
+}  // namespace
+
+// Floats of scratch that `rlis_attention_decode` needs for these sizes (0 when splits == 1).
+extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, int d, int splits) {
+    return splits > 1 ? (long long)n_decode * nh * splits * (d + 2) : 0;
+}
+
+extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                     void* out, float* partial, const int* dec_rows,
+                                     const int* dec_seqs, const int* ctx_lens,
+                                     const int* block_tables, int max_blocks, int n_decode, int nh,
+                                     int nkv, int d, int page_size, float scale, int window,
+                                     int splits, int dtype, cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (dtype != RLIS_BF16 || d % 8 != 0 || d > 256 || d < 8 || nkv <= 0 || nh % nkv != 0 || splits < 1)
+        return RLIS_ERR_UNSUPPORTED;
+    const int nrep = nh / nkv;
+    if (nrep > 8) return RLIS_ERR_UNSUPPORTED;
+    if (splits > 1 && partial == nullptr) return RLIS_ERR_UNSUPPORTED;
+    dim3 grid(nkv, n_decode, splits);
+    const size_t smem = decode_smem_bytes(nrep, d);
+#define LAUNCH(N)                                                                                   \
+    attn_decode_kernel<N><<<grid, DEC_THREADS, smem, stream>>>(                                     \
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows,  \
+        dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, d, page_size, scale, window, splits)
+    switch (nrep) {
+        case 1: LAUNCH(1); break;
+        case 2: LAUNCH(2); break;
+        case 3: LAUNCH(3); break;
+        case 4: LAUNCH(4); break;
+        case 5: LAUNCH(5); break;
+        case 6: LAUNCH(6); break;
+        case 7: LAUNCH(7); break;
+        case 8: LAUNCH(8); break;
+        default: return RLIS_ERR_UNSUPPORTED;
+    }
+#undef LAUNCH
+    int err = RLIS_LAUNCH_CHECK();
+    if (err != 0 || splits == 1) return err;
+    const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
+    attn_decode_combine_kernel<<<dim3(nh, n_decode), threads, 0, stream>>>(partial, (bf16*)out, dec_rows, nh, d, splits);
+    return RLIS_LAUNCH_CHECK();
+}

@@ -8,6 +8,8 @@
 // taken in blocks of 32 that start at a multiple of 32, so the order of every sum depends only on
 // the query's position: the same token gives the same bits however the batch was cut.
 //
+// With a token row list only those tokens of the step are computed (n_tokens = length of the list).
+//
 // This is the kernel of the float32 path and the fallback of the bfloat16 path for shapes that the
 // tensor-core kernels refuse.  Head sizes: multiples of 16 up to 256.
 #include "common.cuh"
@@ -20,18 +22,19 @@ template <typename T>
 __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     T* __restrict__ out, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-    const int* __restrict__ block_tables, int max_blocks, int n_rows, int nh, int nkv, int d,
-    int page_size, float scale, int window) {
+    const int* __restrict__ block_tables, const int* __restrict__ token_rows, int max_blocks,
+    int n_rows, int nh, int nkv, int d, int page_size, float scale, int window) {
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gw = blockIdx.x * WARPS + warp;
     if (gw >= n_rows) return;  // no block-wide barrier below
-    const int t = gw / nh, h = gw - t * nh;
+    const int ti = gw / nh, h = gw - ti * nh;
+    const int t = token_rows != nullptr ? token_rows[ti] : ti;   // a subset of the step's tokens
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
     const int* table = block_tables + (size_t)seq_of_token[t] * max_blocks;
     float* qs = qs_all + warp * d;
-    const T* qrow = q + (size_t)gw * d;
+    const T* qrow = q + ((size_t)t * nh + h) * d;
     for (int j = lane; j < d; j += 32) qs[j] = to_f<T>(qrow[j]);
     __syncwarp();
 
@@ -85,7 +88,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
         }
         m = m_new;
     }
-    T* orow = out + (size_t)gw * d;
+    T* orow = out + ((size_t)t * nh + h) * d;
     const float inv_l = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -97,7 +100,8 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
 
 extern "C" int rlis_attention_generic(const void* q, const void* k_cache, const void* v_cache,
                                       void* out, const int* seq_of_token, const int* positions,
-                                      const int* block_tables, int max_blocks, int n_tokens, int nh,
+                                      const int* block_tables, const int* token_rows,
+                                      int max_blocks, int n_tokens, int nh,
                                       int nkv, int d, int page_size, float scale, int window,
                                       int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -109,11 +113,11 @@ extern "C" int rlis_attention_generic(const void* q, const void* k_cache, const 
     if (dtype == RLIS_F32)
         attn_generic_kernel<float><<<blocks, WARPS * 32, smem, stream>>>(
             (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, seq_of_token,
-            positions, block_tables, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
+            positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
     else if (dtype == RLIS_BF16)
         attn_generic_kernel<bf16><<<blocks, WARPS * 32, smem, stream>>>(
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, seq_of_token,
-            positions, block_tables, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
+            positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -50,6 +50,12 @@ class StepContext:
         self.max_q_len = 0
         self.max_ctx_len = 0
         self.all_decode = False
+        # single decoded tokens and the rest, for the kernels that treat them differently
+        self.n_decode = 0
+        self.dec_rows = self.dec_seqs = None      # int32 [n_decode]: token row, batch entry
+        self.max_decode_ctx = 0
+        self.n_prefill_tokens = 0
+        self.prefill_rows = None                  # int32: rows of the tokens of longer entries
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self._runner.workspace(name, shape, dtype)
@@ -141,7 +147,20 @@ class ModelRunner:
         o_cu = o_ctx + _align4(B)
         o_ss = o_cu + _align4(B + 1)
         o_rows = o_ss + _align4(B)
-        o_bt = o_rows + _align4(max(W, 1))
+        dec_rows, dec_seqs, pf_rows = [], [], []
+        k = 0
+        for b, n in enumerate(lens):
+            if n == 1:
+                dec_rows.append(k)
+                dec_seqs.append(b)
+            else:
+                pf_rows.extend(range(k, k + n))
+            k += n
+        Bd, Tp = len(dec_rows), len(pf_rows)
+        o_dr = o_rows + _align4(max(W, 1))
+        o_ds = o_dr + _align4(max(Bd, 1))
+        o_pr = o_ds + _align4(max(Bd, 1))
+        o_bt = o_pr + _align4(max(Tp if Bd else 0, 1))
         total = o_bt + G * B * mb
         host, dev = self._meta(total)
         if self._upload_done is not None:
@@ -164,6 +183,11 @@ class ModelRunner:
             raise StepError(str(err)) from None
         if W:
             h[o_rows:o_rows + W] = want_rows
+        if Bd:
+            h[o_dr:o_dr + Bd] = dec_rows
+            h[o_ds:o_ds + Bd] = dec_seqs
+            if Tp:
+                h[o_pr:o_pr + Tp] = pf_rows
         dev[:total].copy_(host[:total], non_blocking=True)
         if self._upload_done is None:
             self._upload_done = torch.cuda.Event()
@@ -186,6 +210,13 @@ class ModelRunner:
         st.max_ctx_len = max(s + n for s, n in zip(starts, lens))
         st.all_decode = st.max_q_len == 1
         st.h2d_bytes = total * 4
+        st.n_decode = Bd
+        if Bd:
+            st.dec_rows = dev[o_dr:o_dr + Bd]
+            st.dec_seqs = dev[o_ds:o_ds + Bd]
+            st.max_decode_ctx = max(starts[b] + 1 for b in dec_seqs)
+            st.n_prefill_tokens = Tp
+            st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
         return st
 
     def forward(self, st: StepContext):

@@ -162,11 +162,13 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | N
 def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       out: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                       block_tables: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
-                      page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+                      page_size: int, scale: float, window: int = 0,
+                      token_rows: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention over paged keys and values for any mix of query lengths.
 
     q, out [T, nh d]; caches [pages, nkv, page_size, d]; seq_of_token, positions int32 [T];
-    block_tables int32 [B, max_blocks].  window 0 = all earlier keys."""
+    block_tables int32 [B, max_blocks].  window 0 = all earlier keys.  `token_rows` (int32):
+    compute these rows of the step only."""
     T = q.shape[0]
     _req(q, "q", None, (T, n_heads * head_dim))
     _req(out, "out", q.dtype, (T, n_heads * head_dim))
@@ -182,19 +184,81 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     check(lib().rlis_attention_generic(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         seq_of_token.data_ptr(), positions.data_ptr(), block_tables.data_ptr(),
-        block_tables.shape[1], T, n_heads, n_kv_heads, head_dim, page_size, float(scale),
-        int(window), _code(q.dtype), _stream()), "attention_generic")
+        token_rows.data_ptr() if token_rows is not None else None,
+        block_tables.shape[1], T if token_rows is None else token_rows.shape[0], n_heads,
+        n_kv_heads, head_dim, page_size, float(scale), int(window), _code(q.dtype), _stream()),
+        "attention_generic")
     _count()
+    return out
+
+
+NUM_SMS = 148
+DECODE_MIN_KEYS_PER_SPLIT = 128
+
+
+def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
+    """How many pieces the context is cut into for decode attention: enough CTAs (kv heads x
+    requests x splits) to fill the SMs about four times, each piece at least 128 keys long (role
+    of `split_plan`, crates/model/src/paged_attention.rs:21-36, re-tuned for 148 SMs)."""
+    want = -(-4 * NUM_SMS // max(1, n_decode * n_kv_heads))
+    return max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 64))
+
+
+def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, block_tables,
+                     n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                     window: int, splits: int, scratch: torch.Tensor | None) -> torch.Tensor:
+    """Attention of single decoded tokens (bfloat16): request i's token sits in row dec_rows[i] of
+    q/out and belongs to batch entry dec_seqs[i]; it sees keys 0 .. ctx_lens[seq]-1.  `scratch`:
+    float32, at least n_decode * n_heads * splits * (d + 2) elements when splits > 1."""
+    n = dec_rows.shape[0]
+    _req(q, "q", torch.bfloat16, (None, n_heads * head_dim))
+    _req(out, "out", torch.bfloat16, tuple(q.shape))
+    _req(k_cache, "k_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    _req(v_cache, "v_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    for t, nm in ((dec_rows, "dec_rows"), (dec_seqs, "dec_seqs"), (ctx_lens, "ctx_lens")):
+        _req(t, nm, torch.int32, (None,))
+    _req(block_tables, "block_tables", torch.int32, (None, None))
+    if head_dim % 8 or head_dim > 256 or n_heads % n_kv_heads or n_heads // n_kv_heads > 8:
+        raise KernelError(f"decode attention: head size {head_dim} / group of {n_heads // max(1, n_kv_heads)} "
+                          "heads is not taken (multiples of 8 up to 256, groups up to 8)")
+    if splits > 1:
+        need = n * n_heads * splits * (head_dim + 2)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"decode attention: scratch of {need} float32 elements is needed")
+    check(lib().rlis_attention_decode(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        scratch.data_ptr() if splits > 1 else None, dec_rows.data_ptr(), dec_seqs.data_ptr(),
+        ctx_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n, n_heads,
+        n_kv_heads, head_dim, page_size, float(scale), int(window), int(splits), _code(q.dtype),
+        _stream()), "attention_decode")
+    global launch_count
+    launch_count += 2 if splits > 1 else 1
     return out
 
 
 def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_heads: int,
               head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Attention of every token of the step over its request's cached keys, by the kernel that
-    fits the step (the choice never changes the result beyond rounding)."""
-    return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
-                             step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size,
-                             scale, window)
+    """Attention of every token of the step over its request's cached keys, by the kernels that
+    fit the step: single decoded tokens (bfloat16) go to the split decode kernel, everything else
+    to the kernel for any query length.  The choice never changes the result beyond rounding."""
+    fast_decode = (q.dtype == torch.bfloat16 and step.n_decode > 0 and n_heads // n_kv_heads <= 8
+                   and head_dim % 8 == 0)
+    if not fast_decode:
+        return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
+                                 step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size,
+                                 scale, window)
+    splits = decode_splits(step.n_decode, n_kv_heads, step.max_decode_ctx)
+    scratch = None
+    if splits > 1:
+        scratch = step.buffer("attn_partial", (step.n_decode * n_heads * splits * (head_dim + 2),), torch.float32)
+    attention_decode(q, k_cache, v_cache, out, step.dec_rows, step.dec_seqs, step.ctx_lens,
+                     step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size, scale, window,
+                     splits, scratch)
+    if step.n_prefill_tokens > 0:
+        attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
+                          step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size, scale,
+                          window, token_rows=step.prefill_rows)
+    return out
 
 
 def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

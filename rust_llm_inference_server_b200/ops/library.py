@@ -25,7 +25,8 @@ SIGNATURES = {
     "rlis_swiglu": [P, P, I, I, I, P],
     "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
-    "rlis_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
 }
 

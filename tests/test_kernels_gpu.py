@@ -1,0 +1,326 @@
+"""Each kernel alone against a plain float32 reference of the same op, at other sizes than the
+engine's tiny models use (widths and vocabularies that are no power of two, head sizes 48, 80 and
+112, odd numbers of heads and groups)."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def dev(x):
+    return x.to("cuda")
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embedding(dtype):
+    from rust_llm_inference_server_b200 import ops
+    table = torch.randn(301, 80).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 80, device="cuda")
+    ops.embedding(dev(ids), dev(table), out)
+    assert torch.equal(out.cpu(), P.embedding(ids, table.float()))
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("hidden", [80, 1000, 4100])
+def test_rmsnorm_with_residual_and_rows(dtype, hidden):
+    from rust_llm_inference_server_b200 import ops
+    torch.manual_seed(hidden)
+    T = 7
+    resid, delta = torch.randn(T, hidden) * 3, torch.randn(T, hidden).to(dtype)
+    w = torch.randn(hidden)
+    eps = 3e-6
+    r = dev(resid.clone())
+    out = torch.empty(T, hidden, dtype=dtype, device="cuda")
+    ops.rmsnorm(r, dev(w), eps, out, dev(delta))
+    want_resid = resid + delta.float()
+    assert torch.allclose(r.cpu(), want_resid, atol=1e-6)
+    want = P.rms_norm(want_resid, w, eps)
+    assert (out.float().cpu() - want).abs().max() <= tol(dtype, 2e-5, 5e-2)
+    out2 = torch.empty(T, hidden, dtype=dtype, device="cuda")
+    ops.rmsnorm(r, dev(w), eps, out2)          # no delta: the residual stays
+    assert torch.equal(out2, out) and torch.allclose(r.cpu(), want_resid, atol=1e-6)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    r3 = dev(resid.clone())
+    out3 = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    ops.rmsnorm(r3, dev(w), eps, out3, dev(delta), dev(rows))
+    assert torch.equal(out3, out[rows.long()]) and torch.equal(r3.cpu(), resid)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_swiglu(dtype):
+    from rust_llm_inference_server_b200 import ops
+    gu = (torch.randn(5, 2 * 176) * 3).to(dtype)
+    out = torch.empty(5, 176, dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu), out)
+    g, u = gu.float()[:, :176], gu.float()[:, 176:]
+    want = torch.nn.functional.silu(g) * u
+    # one rounding of the result: half a unit in the last place, 2^-24 or 2^-9 relative
+    rel = 2.0 ** -22 if dtype == torch.float32 else 2.0 ** -8
+    assert bool(((out.float().cpu() - want).abs() <= rel * want.abs() + 1e-6).all())
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (3, 301, 80), (70, 130, 257), (129, 64, 1000)])
+def test_float32_matrix_product_is_true_float32_and_row_independent(shape):
+    from rust_llm_inference_server_b200 import ops
+    M, N, K = shape
+    torch.manual_seed(M)
+    a, w = torch.randn(M, K), torch.randn(N, K)
+    out = ops.gemm_f32(dev(a), dev(w)).cpu()
+    want = (a.double() @ w.double().t())
+    assert (out.double() - want).abs().max() <= 1e-5 * max(1.0, math.sqrt(K))
+    # TF32 would show an error near 1e-3 * |a||w|; and a row's result does not depend on the batch
+    one = ops.gemm_f32(dev(a[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
+    assert torch.equal(one[0], out[M // 2])
+
+
+def cache_from(k, v, page_size, n_pages, seed=0):
+    """Scatters contiguous k, v [(requests) x (len, nkv, d)] into a paged cache with shuffled,
+    interleaved pages; returns caches [pages, nkv, page, d] and the block tables."""
+    rng = np.random.default_rng(seed)
+    nkv, d = k[0].shape[1:]
+    kc = torch.full((n_pages, nkv, page_size, d), float("nan"))
+    vc = torch.full((n_pages, nkv, page_size, d), float("nan"))
+    perm = rng.permutation(n_pages).tolist()
+    max_blocks = max((len(x) + page_size - 1) // page_size for x in k) + 1
+    tables = torch.full((len(k), max_blocks), -1, dtype=torch.int32)
+    for b, (kk, vv) in enumerate(zip(k, v)):
+        for i in range(0, len(kk), page_size):
+            page = perm.pop()
+            tables[b, i // page_size] = page
+            n = min(page_size, len(kk) - i)
+            kc[page, :, :n] = kk[i:i + n].transpose(0, 1)
+            vc[page, :, :n] = vv[i:i + n].transpose(0, 1)
+    return kc, vc, tables
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("geom", [(6, 3, 48, 8), (5, 1, 80, 16), (8, 8, 16, 4), (4, 2, 112, 32)])
+def test_rope_and_cache_write(dtype, geom):
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d, ps = geom
+    torch.manual_seed(nh)
+    T = 9
+    cfg = {"head_dim": d, "rope_theta": 25000.0, "hidden_size": nh * d, "num_attention_heads": nh,
+           "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                            "high_freq_factor": 4.0, "original_max_position_embeddings": 32}}
+    inv = P.inv_freqs(cfg)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d).to(dtype)
+    positions = torch.tensor([0, 1, 2, 3, 100, 4095, 70000, 7, 8], dtype=torch.int32)
+    n_pages = 12
+    slots = torch.tensor([5 * ps + 1, 5 * ps + 2, 0, 11 * ps + ps - 1, 3 * ps, 3 * ps + 1, 7 * ps, 8 * ps + 2, 9 * ps],
+                         dtype=torch.int32)
+    kc = torch.zeros(n_pages, nkv, ps, d, dtype=dtype, device="cuda")
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, nh * d, dtype=dtype, device="cuda")
+    ops.rope_cache(dev(qkv), q_out, kc, vc, dev(positions), dev(slots), dev(inv), nh, nkv, d, ps)
+    x = qkv.float()
+    q = x[:, :nh * d].view(T, nh, d)
+    k = x[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+    v = x[:, (nh + nkv) * d:].view(T, nkv, d)
+    cos, sin = P.rope_tables(inv, positions)
+    t = tol(dtype, 2e-5, 3e-2)   # position 70000: float32 angle, sin/cos of a large argument
+    assert (q_out.float().cpu().view(T, nh, d) - P.apply_rope(q, cos, sin)).abs().max() <= t
+    kr = P.apply_rope(k, cos, sin)
+    for i in range(T):
+        page, off = int(slots[i]) // ps, int(slots[i]) % ps
+        assert (kc[page, :, off].float().cpu() - kr[i]).abs().max() <= t
+        assert torch.equal(vc[page, :, off].float().cpu(), v[i])
+    assert int((kc.float().abs().sum(dim=(1, 3)) > 0).sum()) == T      # nothing else was written
+    # no rotation, nothing stored
+    q2 = torch.empty_like(q_out)
+    ops.rope_cache(dev(qkv), q2, None, None, dev(positions), None, None, nh, nkv, d, ps)
+    assert torch.equal(q2.cpu(), qkv[:, :nh * d])
+
+
+def attention_case(geom, lens, q_lens, page_size, dtype, window=None, seed=0, spike=None):
+    """Requests with `lens` cached tokens each, the last q_lens[b] of them being this step's queries.
+    Returns inputs for the kernels and the plain result [T, nh, d]."""
+    nh, nkv, d = geom
+    g = torch.Generator().manual_seed(seed)
+    ks = [torch.randn(n, nkv, d, generator=g).to(dtype).float() for n in lens]
+    vs = [torch.randn(n, nkv, d, generator=g).to(dtype).float() for n in lens]
+    qs = [torch.randn(m, nh, d, generator=g).to(dtype).float() for m in q_lens]
+    if spike is not None:
+        # one far key carries the whole softmax: it is a scaled copy of the query, and its value
+        # row is the only one that is not small
+        b, qi, key = spike
+        rep = nh // nkv
+        for h in range(nkv):
+            for r in range(1, rep):              # the heads of a group ask the same question
+                qs[b][qi, h * rep + r] = qs[b][qi, h * rep]
+            ks[b][key, h] = (qs[b][qi, h * rep] * 8.0).to(dtype).float()
+        vs[b][key] = 7.0
+    n_pages = sum((n + page_size - 1) // page_size for n in lens) + 3
+    kc, vc, tables = cache_from(ks, vs, page_size, n_pages, seed)
+    want = torch.cat([P.causal_attention(q, k, v, start_pos=len(k) - len(q), window=window)
+                      for q, k, v in zip(qs, ks, vs)])
+    q = torch.cat(qs).reshape(-1, nh * d)
+    seq_of_token = torch.cat([torch.full((m,), b, dtype=torch.int32) for b, m in enumerate(q_lens)])
+    positions = torch.cat([torch.arange(n - m, n, dtype=torch.int32) for n, m in zip(lens, q_lens)])
+    return q.to(dtype), kc.to(dtype), vc.to(dtype), tables, seq_of_token, positions, want
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("geom,ps", [((6, 3, 48), 8), ((5, 1, 80), 16), ((8, 8, 16), 4), ((4, 2, 112), 32),
+                                     ((32, 8, 64), 16), ((7, 7, 256), 16)])
+def test_attention_for_any_query_lengths(dtype, geom, ps):
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d = geom
+    lens, q_lens = [1, 37, 130, 64, 33], [1, 1, 17, 64, 2]
+    q, kc, vc, tables, sot, pos, want = attention_case(geom, lens, q_lens, ps, dtype, seed=nh)
+    out = torch.empty(q.shape, dtype=dtype, device="cuda")
+    ops.attention_generic(dev(q), dev(kc), dev(vc), out, dev(sot), dev(pos), dev(tables), nh, nkv, d, ps,
+                          1 / math.sqrt(d))
+    err = (out.float().cpu().view(-1, nh, d) - want).abs().max()
+    assert err <= tol(dtype, 2e-5, 2e-2), err
+    # a subset of the rows leaves the others untouched
+    out2 = torch.zeros_like(out)
+    rows = torch.tensor([0, 5, 80], dtype=torch.int32)
+    ops.attention_generic(dev(q), dev(kc), dev(vc), out2, dev(sot), dev(pos), dev(tables), nh, nkv, d, ps,
+                          1 / math.sqrt(d), token_rows=dev(rows))
+    assert torch.equal(out2[rows.long()], out[rows.long()])
+    others = torch.ones(out2.shape[0], dtype=torch.bool)
+    others[rows.long()] = False
+    assert float(out2[others.cuda()].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_finds_a_far_key_and_respects_page_edges(dtype):
+    """The softmax sits on one key among hundreds: at a page's first and last slot, in the first
+    page, and just behind the query.  A wrong page or offset would return a wrong value row."""
+    from rust_llm_inference_server_b200 import ops
+    geom, ps = (4, 2, 32), 16
+    for key in (0, 15, 16, 31, 3, 303, 304, 598, 599):
+        q, kc, vc, tables, sot, pos, want = attention_case(geom, [600, 40], [1, 1], ps, dtype, seed=key,
+                                                           spike=(0, 0, key))
+        out = torch.empty(q.shape, dtype=dtype, device="cuda")
+        ops.attention_generic(dev(q), dev(kc), dev(vc), out, dev(sot), dev(pos), dev(tables), 4, 2, 32, ps,
+                              1 / math.sqrt(32))
+        got = out.float().cpu().view(-1, 4, 32)
+        assert (got[0] - 7.0).abs().max() < 0.05, key         # the spiked value row, for every head
+        assert (got - want).abs().max() <= tol(dtype, 1e-4, 3e-2)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_window_edge(dtype):
+    """With a window of W keys the key at position - W + 1 is seen and the one before it is not."""
+    from rust_llm_inference_server_b200 import ops
+    geom, ps, W = (2, 1, 16), 8, 40
+    n = 100
+    for key, seen in ((n - W, True), (n - W - 1, False)):
+        q, kc, vc, tables, sot, pos, want = attention_case(geom, [n], [1], ps, dtype, window=W, seed=3,
+                                                           spike=(0, 0, key))
+        out = torch.empty(q.shape, dtype=dtype, device="cuda")
+        ops.attention_generic(dev(q), dev(kc), dev(vc), out, dev(sot), dev(pos), dev(tables), 2, 1, 16, ps,
+                              0.25, window=W)
+        got = out.float().cpu().view(-1, 2, 16)
+        assert (got - want).abs().max() <= tol(dtype, 1e-4, 3e-2)
+        assert ((got - 7.0).abs().max() < 0.05) == seen
+
+
+@pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((24, 8, 128), 16), ((6, 3, 48), 8), ((5, 1, 80), 16),
+                                     ((8, 8, 16), 4), ((12, 2, 128), 32), ((16, 2, 64), 16), ((7, 7, 256), 64)])
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_decode_attention_split_over_the_context(geom, ps, splits):
+    """Context lengths of the reference's kernel test (1 + (i * 53) % 700, and a few long ones;
+    crates/model/src/paged_attention.rs:423-527), every number of splits, rows in another order
+    than the batch."""
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d = geom
+    lens = [1 + (i * 53) % 700 for i in range(9)] + [1, 32, 33, 2049]
+    B = len(lens)
+    q, kc, vc, tables, sot, pos, want = attention_case(geom, lens, [1] * B, ps, torch.bfloat16, seed=d + splits)
+    order = torch.randperm(B, generator=torch.Generator().manual_seed(1)).to(torch.int32)   # row i holds request order[i]
+    q_rows = q[order.long()].contiguous()
+    out = torch.zeros(B, nh * d, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(B * nh * splits * (d + 2), dtype=torch.float32, device="cuda")
+    ctx = torch.tensor(lens, dtype=torch.int32)
+    inv = torch.empty(B, dtype=torch.int32)
+    inv[order.long()] = torch.arange(B, dtype=torch.int32)
+    # request b's token sits in row inv[b]
+    ops.attention_decode(dev(q_rows), dev(kc), dev(vc), out, dev(inv[torch.arange(B)].contiguous()),
+                         dev(torch.arange(B, dtype=torch.int32)), dev(ctx), dev(tables), nh, nkv, d, ps,
+                         1 / math.sqrt(d), 0, splits, scratch)
+    got = out.float().cpu()[inv.long()].view(B, nh, d)
+    err = (got - want).abs().max()
+    assert err <= 2e-2, err
+
+
+def test_decode_attention_far_key_and_window():
+    from rust_llm_inference_server_b200 import ops
+    geom, ps = (8, 2, 64), 16
+    n = 3000
+    for key, window, seen in ((5, 0, True), (1023, 0, True), (1024, 0, True), (2999, 0, True),
+                              (n - 500, 500, True), (n - 501, 500, False)):
+        q, kc, vc, tables, sot, pos, want = attention_case(geom, [n, 7], [1, 1], ps, torch.bfloat16, seed=key,
+                                                           window=window or None, spike=(0, 0, key))
+        for splits in (1, 7):
+            out = torch.zeros(2, 8 * 64, dtype=torch.bfloat16, device="cuda")
+            scratch = torch.empty(2 * 8 * splits * 66, dtype=torch.float32, device="cuda")
+            ar = dev(torch.arange(2, dtype=torch.int32))
+            ops.attention_decode(dev(q), dev(kc), dev(vc), out, ar, ar, dev(torch.tensor([n, 7], dtype=torch.int32)),
+                                 dev(tables), 8, 2, 64, ps, 0.125, window, splits, scratch)
+            got = out.float().cpu().view(2, 8, 64)
+            assert (got - want).abs().max() <= 3e-2
+            assert ((got[0] - 7.0).abs().max() < 0.05) == seen, (key, window, splits)
+
+
+def test_sample_rows_equals_the_plain_sampler():
+    from rust_llm_inference_server_b200 import ops
+    rng = np.random.default_rng(0)
+    R, V = 7, 1003
+    logits = rng.normal(size=(R, V)).astype(np.float32) * 3
+    logits[0, 5] = logits[0, 900] = logits[0].max() + 1     # a tie: the lowest id wins
+    params = np.zeros((R, 2), dtype=np.uint32)
+    temps = [0.0, 0.0, 0.7, 1.0, 1.5, 0.7, 0.3]
+    keys = [0, 0, P.row_key(1, 10), P.row_key(1, 11), P.row_key(99, 5), P.row_key(2, 10), P.row_key(3, 3)]
+    for r in range(R):
+        if temps[r] > 0:
+            params[r] = (keys[r], np.float32(np.float32(1.0) / np.float32(temps[r])).view(np.uint32))
+    big = np.concatenate([logits, np.zeros((R, 5), np.float32)], axis=1)     # rows with a stride
+    lt = torch.from_numpy(big).cuda()[:, :V]
+    got = ops.sample_rows(lt, torch.from_numpy(params.view(np.int32)).cuda()).cpu().tolist()
+    want = [P.sample_row(logits[r], temps[r], keys[r]) for r in range(R)]
+    assert got == want and got[0] == 5
+    # a row's choice does not depend on its neighbours
+    alone = ops.sample_rows(lt[4:5], torch.from_numpy(params.view(np.int32)[4:5].copy()).cuda()).cpu().tolist()
+    assert alone == [want[4]]
+    # frequencies follow softmax(logits / T)
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]]).cuda().repeat(4000, 1)
+    ps_ = np.zeros((4000, 2), dtype=np.uint32)
+    for i in range(4000):
+        ps_[i] = (P.row_key(7, i), np.float32(1 / 0.7).view(np.uint32))
+    ids = ops.sample_rows(small, torch.from_numpy(ps_.view(np.int32)).cuda()).cpu().numpy()
+    freq = np.bincount(ids, minlength=4) / 4000
+    want_p = np.exp(np.array([0, 1, 2, -1]) / 0.7)
+    assert np.abs(freq - want_p / want_p.sum()).max() < 0.03
+
+
+def test_kernels_refuse_what_they_do_not_take():
+    from rust_llm_inference_server_b200 import ops
+    from rust_llm_inference_server_b200.ops import KernelError
+    x = torch.randn(4, 8)
+    with pytest.raises(KernelError, match="CUDA"):
+        ops.gemm_f32(x, x)                                    # no CPU path
+    with pytest.raises(KernelError, match="contiguous"):
+        ops.gemm_f32(dev(torch.randn(8, 4)).t(), dev(x))
+    with pytest.raises(KernelError, match="multiples of 16"):
+        z = torch.zeros(1, 40, device="cuda")
+        i = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.attention_generic(z, torch.zeros(1, 1, 4, 40, device="cuda"), torch.zeros(1, 1, 4, 40, device="cuda"),
+                              z.clone(), i, i, torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 1, 1, 40, 4, 1.0)
+    with pytest.raises(KernelError, match="not supported"):
+        ops.swiglu(dev(torch.randn(2, 8).half()), dev(torch.randn(2, 4).half()))
