@@ -262,3 +262,44 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
     attn_decode_combine_kernel<<<dim3(nh, n_decode), threads, 0, stream>>>(partial, (bf16*)out, dec_rows, nh, d, splits);
     return RLIS_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_static.h for who needs it and the rules).
+#include "attention_decode_static.h"
+
+// Part of the library image: every GPU that loads the library holds these 8 MiB until exit.
+static __device__ __align__(256) float g_decode_static_scratch[RLIS_DECODE_STATIC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of the array, per device.  In host code `g_decode_static_scratch` is only a
+// stand-in for the symbol, not an address the GPU can use; the address comes from the runtime.
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" long long rlis_attention_decode_static_capacity(void) { return RLIS_DECODE_STATIC_MAX_FLOATS; }
+
+extern "C" int rlis_attention_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                                            void* out, const int* dec_rows, const int* dec_seqs,
+                                            const int* ctx_lens, const int* block_tables,
+                                            int max_blocks, int n_decode, int nh, int nkv, int d,
+                                            int page_size, float scale, int window, int splits,
+                                            int dtype, cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (rlis_attention_decode_scratch_floats(n_decode, nh, d, splits) > RLIS_DECODE_STATIC_MAX_FLOATS)
+        return RLIS_ERR_SCRATCH_TOO_SMALL;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return RLIS_ERR_UNSUPPORTED;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        // First call on this device (it is the current one): look the address up once.
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_ptr[dev] = p;
+    }
+    return rlis_attention_decode(q, k_cache, v_cache, out, g_static_scratch_ptr[dev], dec_rows, dec_seqs,
+                                 ctx_lens, block_tables, max_blocks, n_decode, nh, nkv, d, page_size,
+                                 scale, window, splits, dtype, stream);
+}
