@@ -98,7 +98,12 @@ class LLMEngine:
             raise ValueError(f"kv cache of {cfg.kv_cache_bytes} bytes holds fewer than 2 blocks")
         self.groups = groups
         max_batched = max(cfg.max_batched_tokens, cfg.max_num_seqs)   # engine.rs:265
-        sc = h.SchedulerConfig(cfg.max_num_seqs, max_batched, cfg.policy == "continuous", cfg.prefix_caching)
+        # A request that starts on cached pages skips the tokens they hold; a mixer with state of
+        # its own would miss them, so prefix reuse is off for such models (and, inside the
+        # scheduler, for models with a window group).
+        has_state = any(s is not None for s in model.call_state_specs)
+        sc = h.SchedulerConfig(cfg.max_num_seqs, max_batched, cfg.policy == "continuous",
+                               cfg.prefix_caching and not has_state)
         self.sched = h.Scheduler(sc, [h.GroupConfig(g.num_pages, g.page_size, g.window) for g in groups])
         self.cache = self.sched.cache()
         self.storage = CacheStorage(groups, model.call_state_specs, cfg.max_num_seqs, model.dtype, model.device)

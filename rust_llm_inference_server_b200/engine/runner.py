@@ -45,8 +45,11 @@ class StepContext:
         self.slots: list = []
         self.block_tables: list = []
         self.ctx_lens = self.cu_seqlens = self.state_slots = self.logit_rows = None
-        self.q_lens: list = []
-        self.starts: list = []
+        # host copies, one entry per request of the batch
+        self.q_lens: list = []          # tokens of the request in this step
+        self.starts: list = []          # its tokens already in the cache (0: the request starts here)
+        self.q_starts: list = []        # row of its first token among the step's tokens
+        self.state_slot_ids: list = []  # its fixed-size state slot
         self.max_q_len = 0
         self.max_ctx_len = 0
         self.all_decode = False
@@ -205,6 +208,8 @@ class ModelRunner:
         st.logit_rows = dev[o_rows:o_rows + W] if W else None
         st.q_lens = lens
         st.starts = starts
+        st.state_slot_ids = h[o_ss:o_ss + B].tolist()
+        st.q_starts = h[o_cu:o_cu + B].tolist()
         st.seq_ids = ids
         st.max_q_len = max(lens)
         st.max_ctx_len = max(s + n for s, n in zip(starts, lens))
