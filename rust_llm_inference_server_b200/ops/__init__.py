@@ -275,3 +275,16 @@ def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | 
                                  logits.stride(0), _stream()), "sample_rows")
     _count()
     return out
+
+
+def nll_rows(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Negative log-likelihood of targets[r] under softmax(logits[r]); float32 [R]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise KernelError("nll_rows: logits must be float32 CUDA rows with unit stride")
+    _req(targets, "targets", torch.int32, (R,))
+    out = torch.empty((R,), dtype=torch.float32, device=logits.device)
+    check(lib().rlis_nll_rows(logits.data_ptr(), targets.data_ptr(), out.data_ptr(), R, V,
+                              logits.stride(0), _stream()), "nll_rows")
+    _count()
+    return out

@@ -1,0 +1,159 @@
+"""Each part of a layer alone, built from its spec and a dictionary of tensors, against the plain
+function of the same part: norm, position encoding, attention mixer (with and without a window,
+with and without rotation), feed-forward, and the pre-norm block."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests.plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+class DictSource:
+    def __init__(self, tensors, dtype):
+        self.t, self.dtype = tensors, dtype
+
+    def get(self, name, role="matrix"):
+        x = self.t[name].cuda()
+        return x.to(self.dtype) if role == "matrix" else x.float()
+
+
+class FakeStep:
+    """The fields of a step that parts read, made by hand: requests with `starts[b]` tokens in
+    the cache and `lens[b]` new ones; pages handed out in a scrambled order."""
+
+    def __init__(self, starts, lens, page_size, tables):
+        self.n_seqs, self.n_tokens = len(lens), sum(lens)
+        self.starts, self.q_lens = starts, lens
+        self.q_starts = np.cumsum([0] + lens[:-1]).tolist()
+        pos = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)])
+        sot = np.concatenate([np.full(n, b) for b, n in enumerate(lens)])
+        slots = np.array([tables[b][p // page_size] * page_size + p % page_size for b, p in zip(sot, pos)])
+        i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device="cuda")
+        self.positions, self.seq_of_token, self.slots = i32(pos), i32(sot), [i32(slots)]
+        width = max(len(t) for t in tables)
+        self.block_tables = [i32([list(t) + [-1] * (width - len(t)) for t in tables])]
+        self.ctx_lens = i32([s + n for s, n in zip(starts, lens)])
+        dec = [b for b, n in enumerate(lens) if n == 1]
+        self.n_decode = len(dec)
+        self.dec_seqs = i32(dec) if dec else None
+        self.dec_rows = i32([self.q_starts[b] for b in dec]) if dec else None
+        self.max_decode_ctx = max([starts[b] + 1 for b in dec], default=0)
+        rows = [r for b, n in enumerate(lens) if n > 1 for r in range(self.q_starts[b], self.q_starts[b] + n)]
+        self.n_prefill_tokens = len(rows) if dec else 0
+        self.prefill_rows = i32(rows) if (dec and rows) else None
+        self._bufs = {}
+
+    def buffer(self, name, shape, dtype):
+        return torch.empty(tuple(shape), dtype=dtype, device="cuda")
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 3e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_and_feed_forward_parts(dtype):
+    from rust_llm_inference_server_b200.parts import RMSNormSpec, SwiGLUSpec, build_feed_forward, build_norm
+    torch.manual_seed(0)
+    H, I, T = 80, 176, 6
+    w = {"n": torch.randn(H) * 0.1 + 1, "g": torch.randn(I, H) * 0.1, "u": torch.randn(I, H) * 0.1,
+         "d": torch.randn(H, I) * 0.1}
+    if dtype == torch.bfloat16:
+        w = {k: v.bfloat16().float() for k, v in w.items()}
+    src = DictSource(w, dtype)
+    step = FakeStep([0], [T], 8, [[0]])
+    norm = build_norm(RMSNormSpec(H, 3e-6, "n"), dtype, "cuda")
+    assert norm.tensors() == {"n": (H,)}
+    norm.load(src)
+    resid, delta = torch.randn(T, H), torch.randn(T, H).to(dtype)
+    r = resid.cuda()
+    out = norm.forward(r, delta.cuda(), step)
+    want = P.rms_norm(resid + delta.float(), w["n"], 3e-6)
+    assert (out.float().cpu() - want).abs().max() <= tol(dtype) and out.dtype == dtype
+    ffn = build_feed_forward(SwiGLUSpec(H, I, "g", "u", "d"), dtype, "cuda")
+    assert ffn.tensors() == {"g": (I, H), "u": (I, H), "d": (H, I)}
+    ffn.load(src)
+    x = torch.randn(T, H).to(dtype)
+    got = ffn.forward(x.cuda(), step)
+    want = P.swiglu_mlp(x.float(), {"p.gate_proj.weight": w["g"], "p.up_proj.weight": w["u"],
+                                    "p.down_proj.weight": w["d"]}, "p.")
+    assert (got.float().cpu() - want).abs().max() <= tol(dtype) * 3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,rotate", [(None, True), (5, True), (None, False)])
+def test_attention_part_over_two_steps(dtype, window, rotate):
+    """A portion of a prompt in one step, the rest beside a decoded token of another request in
+    the next: the part's output equals plain attention over the whole sequences."""
+    from rust_llm_inference_server_b200.parts import (GQAAttentionSpec, KVCacheSpec, LayerCache, NoPositionSpec,
+                                                      RopeSpec, build_mixer)
+    torch.manual_seed(1)
+    H, nh, nkv, d, ps = 80, 6, 2, 16, 4
+    cfg = {"head_dim": d, "rope_theta": 777.0, "hidden_size": H, "num_attention_heads": nh,
+           "num_key_value_heads": nkv}
+    w = {"q": torch.randn(nh * d, H) * 0.2, "k": torch.randn(nkv * d, H) * 0.2, "v": torch.randn(nkv * d, H) * 0.2,
+         "o": torch.randn(H, nh * d) * 0.2}
+    if dtype == torch.bfloat16:
+        w = {k: v.bfloat16().float() for k, v in w.items()}
+    spec = GQAAttentionSpec(H, nh, nkv, d, "q", "k", "v", "o",
+                            position=RopeSpec(d, 777.0, None) if rotate else NoPositionSpec(), window=window)
+    att = build_mixer(spec, dtype, "cuda")
+    assert att.cache_spec() == KVCacheSpec(nkv, d, window) and att.state_spec() is None
+    att.load(DictSource(w, dtype))
+    n_a, n_b = 11, 7
+    xa, xb = torch.randn(n_a, H).to(dtype), torch.randn(n_b, H).to(dtype)
+    pool = torch.zeros(2, 9, nkv, ps, d, dtype=dtype, device="cuda")
+    cache = LayerCache(pool[0], pool[1], 0, ps)
+    tables = [[7, 2, 5], [0, 8]]
+    # step 1: tokens 0..5 of A and 0..5 of B;  step 2: tokens 6..10 of A beside the last token of B
+    s1 = FakeStep([0, 0], [6, 6], ps, tables)
+    o1 = att.forward(torch.cat([xa[:6], xb[:6]]).cuda(), s1, cache, None)
+    s2 = FakeStep([6, 6], [5, 1], ps, tables)
+    o2 = att.forward(torch.cat([xa[6:], xb[6:]]).cuda(), s2, cache, None)
+    got_a = torch.cat([o1[:6], o2[:5]]).float().cpu()
+    got_b = torch.cat([o1[6:], o2[5:]]).float().cpu()
+
+    def plain(x):
+        n = x.shape[0]
+        q = P.linear(x, w["q"]).view(n, nh, d)
+        k = P.linear(x, w["k"]).view(n, nkv, d)
+        v = P.linear(x, w["v"]).view(n, nkv, d)
+        if dtype == torch.bfloat16:            # the product's output is stored in bfloat16
+            q, k, v = (t.bfloat16().float() for t in (q, k, v))
+        if rotate:
+            cos, sin = P.rope_tables(P.inv_freqs(cfg), torch.arange(n))
+            q, k = P.apply_rope(q, cos, sin), P.apply_rope(k, cos, sin)
+        o = P.causal_attention(q, k, v, 0, window=window).reshape(n, nh * d)
+        return P.linear(o, w["o"])
+
+    for got, x in ((got_a, xa), (got_b, xb)):
+        err = (got - plain(x.float())).abs().max()
+        assert err <= tol(dtype) * 2, err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prenorm_block(dtype):
+    from rust_llm_inference_server_b200.config import LlamaConfig
+    from rust_llm_inference_server_b200.models.llama import describe_llama
+    from rust_llm_inference_server_b200.parts import LayerCache, build_block
+    from rust_llm_inference_server_b200.weights import random_tensors
+    from tests.tiny_configs import TINY_C
+    cfg = LlamaConfig.from_dict(TINY_C)
+    w = {k: v.float() for k, v in random_tensors(TINY_C, 5).items()}
+    blk = build_block(describe_llama(cfg).layers[1], dtype, "cuda")
+    for part in blk.parts():
+        part.load(DictSource(w, dtype))
+    T, ps = 13, 8
+    x = torch.randn(T, cfg.hidden_size)
+    pool = torch.zeros(2, 4, cfg.num_key_value_heads, ps, cfg.head_dim, dtype=dtype, device="cuda")
+    step = FakeStep([0], [T], ps, [[3, 1]])
+    resid = x.cuda()
+    resid, delta = blk.forward(resid, None, step, LayerCache(pool[0], pool[1], 0, ps), None)
+    got = resid.cpu() + delta.float().cpu()
+    want = P.decoder_layer(x, w, 1, TINY_C, torch.arange(T))
+    assert (got - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
