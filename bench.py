@@ -191,6 +191,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length at the last timed decode step")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill"],
+                    help="run one part only and print a short line (for profiler captures of a small case)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -213,8 +216,11 @@ def main() -> int:
     total = args.warmup + args.steps
     page = 16
     max_b = max(B, 64)
-    pool_tokens = max_b * (CONTEXT + page)
-    llm = LLM.from_random(cfg, SEED, dtype="bfloat16", on_device=True, max_seq_len=CONTEXT + page,
+    context = args.context
+    if args.only:
+        max_b = B
+    pool_tokens = max_b * (context + page)
+    llm = LLM.from_random(cfg, SEED, dtype="bfloat16", on_device=True, max_seq_len=max(context, PREFILL_TOKENS) + page,
                           num_blocks=pool_tokens // page + 64, block_size=page, max_num_seqs=max_b,
                           max_batched_tokens=max(2048, max_b), prefix_caching=False)
     runner = llm.engine.runner
@@ -224,8 +230,13 @@ def main() -> int:
     rng = np.random.default_rng(0)
     V = cfg["vocab_size"]
     cache = llm.engine.cache
+    if args.only == "decode":
+        ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch)
+        print(json.dumps({"only": "decode", "batch": B, "context": context, "ms_per_step": round(ms, 4),
+                          "launches_per_step": launches}))
+        return 0
     pre_ms = []
-    for it in range(5):
+    for it in range(5 if not args.only else args.warmup + args.steps):
         sid = 500 + it
         cache.acquire_state_slot(sid)
         assert cache.reserve(sid, PREFILL_TOKENS)
@@ -238,7 +249,10 @@ def main() -> int:
         torch.cuda.synchronize()
         pre_ms.append(s.elapsed_time(e))
         cache.free(sid)
-    prefill_ms = statistics.median(pre_ms[2:])
+    prefill_ms = statistics.median(pre_ms[2:] if not args.only else pre_ms[args.warmup:])
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)}))
+        return 0
     pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3),
@@ -247,21 +261,21 @@ def main() -> int:
     # ---- decode points at batch 1 and 64, then the headline batch under the clock sampler ----
     points = {}
     for b in (1, 64):
-        ms, _ = decode_run(llm, b, max(16, args.steps // 2), args.warmup, CONTEXT, torch)
+        ms, _ = decode_run(llm, b, max(16, args.steps // 2), args.warmup, context, torch)
         points[f"decode_b{b}"] = round(b / (ms / 1e3), 1)
     clocks = ClockSampler()
     clocks.start()
-    ms, launches = decode_run(llm, B, args.steps, args.warmup, CONTEXT, torch)
+    ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch)
     clk = clocks.stop()
     value = B / (ms / 1e3)
-    mean_ctx = CONTEXT - args.steps / 2
+    mean_ctx = context - args.steps / 2
     step_bytes = weight_bytes(cfg, n_layers) + B * mean_ctx * kv_bytes_per_token(cfg, n_layers)
     achieved = step_bytes / (ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
 
     # ---- end to end through the Python entry point ----
-    prompts = [rng.integers(0, V, size=CONTEXT - total - 1).tolist() for _ in range(B)]
+    prompts = [rng.integers(0, V, size=context - total - 1).tolist() for _ in range(B)]
     sp = SamplingParams(max_tokens=total + 1, ignore_eos=True)
     eng = llm.engine
     h2d0 = d2h0 = 0
@@ -294,7 +308,7 @@ def main() -> int:
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": V,
             "tied": True, "rope": "theta 5e5 llama3 32/1/4/8192", "eps": 1e-5,
-            "global_batch": B, "seq_len": CONTEXT, "page_size": page, "parallelism": "single GPU",
+            "global_batch": B, "seq_len": context, "page_size": page, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (weights 2.47 GB per step)", "kv_dtype": "bf16",
         },
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,

@@ -111,6 +111,7 @@ class LLMEngine:
         # can hold with the watermark to spare (engine.rs:263-280)
         self.max_seq_len = int(min(cfg.max_seq_len, model.spec.max_positions, self.cache.max_seq_tokens()))
         self.runner = ModelRunner(model, self.cache, self.storage, self.max_seq_len)
+        self.runner.use_graphs = bool(cfg.cuda_graphs)
         self.eos_ids = set(model.spec.eos_token_ids)
         self.seqs: dict[int, _Sequence] = {}
         self._next_id = 0

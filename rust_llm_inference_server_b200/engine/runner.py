@@ -79,7 +79,12 @@ class ModelRunner:
         self._ws: dict[str, torch.Tensor] = {}
         self._meta_host = None
         self._meta_dev = None
-        self._graph_keepalive: list = []
+        # CUDA graphs of decode-only steps, by (batch, wanted rows, split plan); dropped whenever
+        # a buffer they point into is replaced by a larger one
+        self.use_graphs = True
+        self._graphs: dict = {}
+        self._graph_seen: set = set()
+        self._graph_pool = None
         self._upload_done = None
         self._graph_launches = 0
 
@@ -92,17 +97,19 @@ class ModelRunner:
         buf = self._ws.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < n:
             cap = max(n, 2 * buf.numel() if buf is not None and buf.dtype == dtype else n)
-            if buf is not None:
-                self._graph_keepalive.append(buf)
+            self._drop_graphs()         # captured graphs point at the old buffer
             buf = torch.empty((cap,), dtype=dtype, device=self.device)
             self._ws[name] = buf
         return buf[:n].view(*shape)
 
+    def _drop_graphs(self) -> None:
+        self._graphs.clear()
+        self._graph_pool = None         # a pool dies with its last graph; the next capture opens a new one
+
     def _meta(self, n: int):
         if self._meta_host is None or self._meta_host.numel() < n:
             cap = max(n, 1 << 16)
-            if self._meta_dev is not None:
-                self._graph_keepalive.append(self._meta_dev)
+            self._drop_graphs()
             self._meta_host = torch.empty((cap,), dtype=torch.int32, pin_memory=True)
             self._meta_dev = torch.empty((cap,), dtype=torch.int32, device=self.device)
         return self._meta_host, self._meta_dev
@@ -224,12 +231,51 @@ class ModelRunner:
             st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
         return st
 
-    def forward(self, st: StepContext):
-        """Launches the model on a prepared step; float32 logits [wanted, vocab] or None."""
+    def _forward_eager(self, st: StepContext):
         resid, delta = self.model.forward(st, self._caches, self._states)
         if st.logit_rows is None:
             return None
         return self.model.logits(resid, delta, st, st.logit_rows)
+
+    def _graph_key(self, st: StepContext):
+        """Decode-only steps of a model whose parts read nothing from the host run from a captured
+        graph: the launch-bound inner loop of generation (about ten kernels a layer)."""
+        if not (self.use_graphs and st.all_decode and self.model.graph_safe):
+            return None
+        W = 0 if st.logit_rows is None else st.logit_rows.shape[0]
+        # the only way the contexts' lengths reach the launch configuration (ops.decode_splits)
+        return (st.n_seqs, W, min(st.max_decode_ctx // ops.DECODE_MIN_KEYS_PER_SPLIT, 64))
+
+    def forward(self, st: StepContext):
+        """Launches the model on a prepared step; float32 logits [wanted, vocab] or None.  The
+        logits of a step replayed from a graph live in that graph's output buffer until the next
+        step with the same shape."""
+        key = self._graph_key(st)
+        if key is None:
+            return self._forward_eager(st)
+        entry = self._graphs.get(key)
+        if entry is None:
+            if key not in self._graph_seen:
+                # first sight: run eagerly, which also sizes every scratch buffer for this shape
+                self._graph_seen.add(key)
+                return self._forward_eager(st)
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self._forward_eager(st)
+            n = ops.launch_count - before
+            ops.launch_count = before           # capturing launches nothing
+            if key not in self._graph_seen or not self.use_graphs:
+                return self._forward_eager(st)
+            entry = (graph, logits, n)
+            self._graphs[key] = entry
+        graph, logits, n = entry
+        graph.replay()
+        self._graph_launches += n
+        return logits
 
     def step(self, entries: list):
         return self.forward(self.prepare(entries))

@@ -42,6 +42,10 @@ class Model:
         self.embed = None
         self.lm_head = None
         self._plan_caches()
+        # whether a step of this model can be captured in a CUDA graph: every part launches the
+        # same kernels on the same device buffers whatever the host-side lists of the step hold
+        self.graph_safe = all(getattr(p, "graph_safe", False) for blk in self.blocks for p in blk.parts()) \
+            and getattr(self.final_norm, "graph_safe", False)
 
     # ---- what the cache manager has to provide ----
 

@@ -18,6 +18,8 @@ class GQAAttention(Mixer):
     Scores, softmax and the value sum are float32 in every kernel.  Query head h reads key/value
     head h // (n_heads // n_kv_heads) (attention.rs:166-175)."""
 
+    graph_safe = True    # launches depend on the step's device arrays and shapes only
+
     def __init__(self, spec, dtype, device):
         self.spec = spec
         self.dtype = dtype

@@ -25,6 +25,10 @@ class TensorSource:
 
 
 class Part:
+    # True when `forward` reads only device arrays and shapes of the step (never its host-side
+    # lists), so that a decode step can be replayed from a captured CUDA graph.
+    graph_safe = False
+
     def tensors(self) -> dict:
         """Checkpoint tensors this part reads: {name: shape}."""
         return {}

@@ -12,6 +12,8 @@ class SwiGLU(FeedForward):
     """gate and up are stacked into one (2I, hidden) matrix at load time, so one product feeds the
     gating kernel; a pure change of layout."""
 
+    graph_safe = True    # launches depend on the step's device arrays and shapes only
+
     def __init__(self, spec, dtype, device):
         self.spec = spec
         self.dtype = dtype

@@ -13,6 +13,8 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * w.  eps is used as a float32 (layers.rs:115); the sum of
     squares and the scale are float32; the weight is held in float32 (an exact widening)."""
 
+    graph_safe = True    # launches depend on the step's device arrays and shapes only
+
     def __init__(self, spec, dtype, device):
         self.dim = spec.dim
         self.eps = float(np.float32(spec.eps))
