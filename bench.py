@@ -137,7 +137,7 @@ def run_reference(args) -> int:
     return 0
 
 
-def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch):
+def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: bool = True):
     """Device-timed decode: B requests, each step one teacher-forced token per request and the
     sampler kernel; the last step's context is `ctx_end`.  Returns (ms per step, launches per step)."""
     import numpy as np
@@ -156,7 +156,7 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch):
         assert cache.reserve(sid, ctx_end), "cache pool too small for the benchmark"
     # fill the cache up to ctx0 with a prompt cut into portions of at most 2,048 tokens
     for sid in ids:
-        pos = 0
+        pos = 0 if fill else ctx0      # (profiler captures skip the fill: the pages then hold zeros)
         while pos < ctx0:
             n = min(2048, ctx0 - pos)
             runner.step([StepEntry(sid, rng.integers(0, V, size=n).tolist(), pos, [])])
@@ -192,6 +192,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at the last timed decode step")
+    ap.add_argument("--no-fill", action="store_true",
+                    help="with --only decode: do not compute the cached context first (keeps profiler captures short)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run one part only and print a short line (for profiler captures of a small case)")
     args = ap.parse_args()
@@ -231,7 +233,7 @@ def main() -> int:
     V = cfg["vocab_size"]
     cache = llm.engine.cache
     if args.only == "decode":
-        ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch)
+        ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch, fill=not args.no_fill)
         print(json.dumps({"only": "decode", "batch": B, "context": context, "ms_per_step": round(ms, 4),
                           "launches_per_step": launches}))
         return 0

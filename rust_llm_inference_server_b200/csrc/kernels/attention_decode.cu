@@ -16,6 +16,7 @@
 // Scratch: when splits > 1 the kernel writes partial results [request, head, split, d + 2] float32
 // to a caller-provided buffer and `attention_decode_combine` merges them.
 #include "common.cuh"
+#include "mma_utils.cuh"
 #include <math.h>
 
 namespace {
@@ -191,6 +192,218 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
     }
 }
 
+// Tensor-core version for head sizes 64 and 128 (groups of up to 8 query heads).  The CUDA-core
+// kernel above needs about 750 lane-instructions per key and kv head, which caps it near a fifth of
+// the HBM rate; here the heads of a group are the rows of an m16n8k16 tile, so a key costs a few
+// tensor instructions and the kernel waits on memory only.
+//
+// Per warp: blocks of 32 keys, double-buffered in shared memory by 16-byte asynchronous copies
+// (rows padded to D + 8 elements, which keeps ldmatrix free of bank conflicts).
+//   S[heads x 32 keys] = Q K^T      (K rows through ldmatrix, bf16 products, float32 sums)
+//   online softmax in float32 on S * scale
+//   O[heads x D]      += P V        (P rounded to bf16 as the A operand, V through ldmatrix.trans)
+template <int D>
+__global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
+    const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
+    const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
+    float scale, int window, int splits) {
+    constexpr int STRIDE = D + 8;            // elements per padded row
+    constexpr int KS = D / 16;               // k-steps of Q K^T
+    constexpr int ND = D / 8;                // n-tiles of P V
+    constexpr int CPR = D / 8;               // 16-byte chunks per row
+    constexpr int TILE = 32 * STRIDE;        // elements of one K or V tile
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 4 * TILE;   // [stage][K|V][32][STRIDE]
+
+    const int kvh = blockIdx.x, bi = blockIdx.y, split = blockIdx.z;
+    const int row = dec_rows[bi];
+    const int seq = dec_seqs[bi];
+    const int ctx = ctx_lens[seq];
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const int lo_all = window > 0 ? max(0, ctx - window) : 0;
+    const int first_blk = lo_all >> 5;
+    const int n_blk = ((ctx + 31) >> 5) - first_blk;
+    const int blk_per_split = (n_blk + splits - 1) / splits;
+    const int blk0 = first_blk + split * blk_per_split;
+    const int blk1 = min(blk0 + blk_per_split, first_blk + n_blk);
+    const size_t head_stride = (size_t)page_size * D;
+
+    // Q as A fragments: row g = head g of the group (rows >= nrep and rows 8..15 are zero)
+    uint32_t qa[KS][4];
+    {
+        const bf16* qrow = q + ((size_t)row * nh + kvh * nrep + (g < nrep ? g : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
+            qa[ks][1] = 0u;
+            qa[ks][2] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c + 8) : 0u;
+            qa[ks][3] = 0u;
+        }
+    }
+
+    auto issue = [&](int blk, int stage) {
+        bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
+        bf16* vs_ = ks_ + TILE;
+#pragma unroll
+        for (int i = 0; i < CPR; ++i) {               // 32 * CPR chunks, 32 lanes
+            const int chunk = i * 32 + lane;
+            const int key_in = chunk / CPR, c16 = chunk % CPR;
+            const int key = (blk << 5) + key_in;
+            const bool valid = key >= lo_all && key < ctx;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[key / page_size];
+                off = ((size_t)page * nkv + kvh) * head_stride + (size_t)(key % page_size) * D + c16 * 8;
+            }
+            cp_async16(ks_ + key_in * STRIDE + c16 * 8, k_cache + off, valid);
+            cp_async16(vs_ + key_in * STRIDE + c16 * 8, v_cache + off, valid);
+        }
+        cp_async_commit();
+    };
+
+    float m_run = -INFINITY, l_run = 0.f;      // of row g (every lane of a quad holds a copy)
+    float oacc[ND][4];
+#pragma unroll
+    for (int nd = 0; nd < ND; ++nd)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[nd][e] = 0.f;
+
+    int blk = blk0 + warp;
+    int stage = 0;
+    if (blk < blk1) issue(blk, 0);
+    while (blk < blk1) {
+        const int nblk = blk + DEC_WARPS;
+        if (nblk < blk1) {
+            issue(nblk, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
+        const bf16* vs_ = ks_ + TILE;
+
+        float sacc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+#pragma unroll
+            for (int ks2 = 0; ks2 < KS / 2; ++ks2) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, ks_ + (nt * 8 + (lane & 7)) * STRIDE + ks2 * 32 + (lane >> 3) * 8);
+                mma_bf16_16816(sacc[nt], qa[2 * ks2], kb[0], kb[1]);
+                mma_bf16_16816(sacc[nt], qa[2 * ks2 + 1], kb[2], kb[3]);
+            }
+        }
+        // softmax over this block for row g
+        float p[4][2];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = (blk << 5) + nt * 8 + 2 * c + e;
+                const float sv = (key >= lo_all && key < ctx) ? sacc[nt][e] * scale : -INFINITY;
+                p[nt][e] = sv;
+                mx = fmaxf(mx, sv);
+            }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);          // finite: every block holds a visible key
+        const float corr = expf(m_run - m_new);
+        float lsum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p[nt][e] = expf(p[nt][e] - m_new);
+                lsum += p[nt][e];
+            }
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+        lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+        l_run = l_run * corr + lsum;
+        m_run = m_new;
+#pragma unroll
+        for (int nd = 0; nd < ND; ++nd) {
+            oacc[nd][0] *= corr;
+            oacc[nd][1] *= corr;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+            pa[1] = 0u;
+            pa[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+            pa[3] = 0u;
+#pragma unroll
+            for (int nd2 = 0; nd2 < ND / 2; ++nd2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3;
+                ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * STRIDE + (nd2 * 2 + (mat >> 1)) * 8);
+                mma_bf16_16816(oacc[2 * nd2], pa, vb[0], vb[1]);
+                mma_bf16_16816(oacc[2 * nd2 + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncwarp();                                   // the stage may be overwritten from here on
+        blk = nblk;
+        stage ^= 1;
+    }
+
+    // merge the warps through shared memory (the tiles are no longer needed)
+    __syncthreads();
+    float* merge = reinterpret_cast<float*>(smem_raw);          // [DEC_WARPS][nrep][D]
+    float* ml = merge + (size_t)DEC_WARPS * nrep * D;           // [DEC_WARPS][nrep][2]
+    if (g < nrep) {
+        float* mo = merge + ((size_t)warp * nrep + g) * D;
+#pragma unroll
+        for (int nd = 0; nd < ND; ++nd) {
+            mo[nd * 8 + 2 * c] = oacc[nd][0];
+            mo[nd * 8 + 2 * c + 1] = oacc[nd][1];
+        }
+        if (c == 0) {
+            ml[(warp * nrep + g) * 2] = m_run;
+            ml[(warp * nrep + g) * 2 + 1] = l_run;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nrep * D; i += DEC_THREADS) {
+        const int h = i / D, j = i - h * D;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) big = fmaxf(big, ml[(w * nrep + h) * 2]);
+        float a = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = ml[(w * nrep + h) * 2];
+            if (mw == -INFINITY) continue;              // this warp had no block of keys
+            const float wgt = expf(mw - big);
+            a += merge[((size_t)w * nrep + h) * D + j] * wgt;
+            lsum += ml[(w * nrep + h) * 2 + 1] * wgt;
+        }
+        const int head = kvh * nrep + h;
+        if (splits == 1) {
+            out[((size_t)row * nh + head) * D + j] = from_f<bf16>(a / lsum);
+        } else {
+            float* pr = partial + (((size_t)bi * nh + head) * splits + split) * (D + 2);
+            pr[j] = a;
+            if (j == 0) {
+                pr[D] = big;
+                pr[D + 1] = lsum;
+            }
+        }
+    }
+}
+
+template <int D> constexpr size_t decode_mma_smem_bytes() {
+    return (size_t)DEC_WARPS * 4 * 32 * (D + 8) * sizeof(bf16);
+}
+
 // Merges the splits: big = max m over non-empty splits, w = exp(m - big),
 // out = sum acc * w / sum l * w (crates/model/src/paged_attention.metal:276-304).
 __global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
@@ -240,11 +453,35 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
     if (splits > 1 && partial == nullptr) return RLIS_ERR_UNSUPPORTED;
     dim3 grid(nkv, n_decode, splits);
     const size_t smem = decode_smem_bytes(nrep, d);
+    bool launched = false;
+    if (d == 64 || d == 128) {
+        static bool attr_done[2] = {false, false};
+        if (d == 64) {
+            if (!attr_done[0]) {
+                cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)decode_mma_smem_bytes<64>());
+                attr_done[0] = true;
+            }
+            attn_decode_mma_kernel<64><<<grid, DEC_THREADS, decode_mma_smem_bytes<64>(), stream>>>(
+                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits);
+        } else {
+            if (!attr_done[1]) {
+                cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)decode_mma_smem_bytes<128>());
+                attr_done[1] = true;
+            }
+            attn_decode_mma_kernel<128><<<grid, DEC_THREADS, decode_mma_smem_bytes<128>(), stream>>>(
+                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits);
+        }
+        launched = true;
+    }
 #define LAUNCH(N)                                                                                   \
     attn_decode_kernel<N><<<grid, DEC_THREADS, smem, stream>>>(                                     \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows,  \
         dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, d, page_size, scale, window, splits)
-    switch (nrep) {
+    if (!launched) switch (nrep) {
         case 1: LAUNCH(1); break;
         case 2: LAUNCH(2); break;
         case 3: LAUNCH(3); break;
