@@ -87,15 +87,16 @@ def rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Te
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """out[t, i] = silu(gate_i) * up_i; gate_up [T, 2I], out [T, I].  interleave 0: gate columns
+    first, then up columns; B > 0: blocks of B gate columns each followed by their B up columns."""
     T, I2 = gate_up.shape
     if I2 % 2:
         raise KernelError(f"swiglu: the fused gate|up width must be even, got {I2}")
     _req(gate_up, "gate_up")
     _req(out, "out", gate_up.dtype, (T, I2 // 2))
-    check(lib().rlis_swiglu(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, _code(out.dtype),
-                            _stream()), "swiglu")
+    check(lib().rlis_swiglu(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, int(interleave),
+                            _code(out.dtype), _stream()), "swiglu")
     _count()
     return out
 
@@ -115,16 +116,38 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+SKINNY_MAX_ROWS = 16
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False) -> torch.Tensor:
+    """y = x @ w^T for at most 16 rows of bfloat16 x: the weight-streaming tensor-core kernel of
+    the decode step.  `swiglu4`: w is a gate|up matrix interleaved in blocks of 4 rows and the
+    result is silu(gate) * up, [M, N / 2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    _req(x, "x", torch.bfloat16)
+    _req(w, "w", torch.bfloat16, (N, K))
+    if M > SKINNY_MAX_ROWS or K % 8 or (swiglu4 and N % 8):
+        raise KernelError(f"skinny_gemm: takes up to {SKINNY_MAX_ROWS} rows and K a multiple of 8, got M={M}, K={K}")
+    out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
+    check(lib().rlis_skinny_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
+                                      1 if swiglu4 else 0, _stream()), "skinny_gemm")
+    _count()
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
-    """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: the
-    library GEMM with float32 accumulation; `out_dtype=torch.float32` keeps the accumulator's
-    precision (used for logits)."""
+    """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
+    16 rows go to this package's weight-streaming kernel, more to the library GEMM; both
+    accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits)."""
     if x.dtype == torch.float32:
         return gemm_f32(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: expected matching float32 or bfloat16 operands, got {x.dtype}, {w.dtype}")
     if not x.is_cuda:
         raise KernelError("linear: expected CUDA tensors; there is no CPU path")
+    if x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+        return skinny_gemm(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

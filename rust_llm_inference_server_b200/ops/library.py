@@ -22,7 +22,8 @@ LL = c_longlong
 SIGNATURES = {
     "rlis_embedding": [P, P, P, I, I, I, I, P],
     "rlis_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
-    "rlis_swiglu": [P, P, I, I, I, P],
+    "rlis_swiglu": [P, P, I, I, I, I, P],
+    "rlis_skinny_gemm_bf16": [P, P, P, I, I, I, I, I, P],
     "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],

@@ -9,8 +9,9 @@ from .base import FeedForward, register_feed_forward
 
 
 class SwiGLU(FeedForward):
-    """gate and up are stacked into one (2I, hidden) matrix at load time, so one product feeds the
-    gating kernel; a pure change of layout."""
+    """gate and up are stacked into one (2I, hidden) matrix at load time, rows interleaved in
+    blocks of 4 (4 gate rows, their 4 up rows, ...), so one product feeds the gating and the
+    decode kernel can gate in its epilogue; a pure change of layout."""
 
     graph_safe = True    # launches depend on the step's device arrays and shapes only
 
@@ -27,13 +28,23 @@ class SwiGLU(FeedForward):
 
     def load(self, src) -> None:
         s = self.spec
-        self.w_gate_up = torch.cat([src.get(s.gate_proj), src.get(s.up_proj)], dim=0).contiguous()
+        g, u = src.get(s.gate_proj), src.get(s.up_proj)
+        self.interleave = 4 if s.intermediate % 4 == 0 else 0
+        if self.interleave:
+            self.w_gate_up = torch.stack([g.view(-1, 4, s.hidden), u.view(-1, 4, s.hidden)], dim=1) \
+                .reshape(2 * s.intermediate, s.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = src.get(s.down_proj).contiguous()
 
     def forward(self, x, step):
-        gu = ops.linear(x, self.w_gate_up)
-        act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
-        ops.swiglu(gu, act)
+        if (self.dtype == torch.bfloat16 and self.interleave == 4 and x.shape[0] <= ops.SKINNY_MAX_ROWS
+                and self.spec.hidden % 8 == 0):
+            act = ops.skinny_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
+        else:
+            gu = ops.linear(x, self.w_gate_up)
+            act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
+            ops.swiglu(gu, act, self.interleave)
         return ops.linear(act, self.w_down)
 
 

@@ -86,6 +86,44 @@ def test_float32_matrix_product_is_true_float32_and_row_independent(shape):
     assert torch.equal(one[0], out[M // 2])
 
 
+@pytest.mark.parametrize("shape", [(1, 8, 8), (8, 3072, 2048), (3, 301, 80), (16, 520, 176), (13, 64, 8200), (5, 1000, 96)])
+def test_skinny_product_for_decode_rows(shape):
+    from rust_llm_inference_server_b200 import ops
+    M, N, K = shape
+    torch.manual_seed(N)
+    x, w = torch.randn(M, K).bfloat16(), (torch.randn(N, K) * 0.05).bfloat16()
+    want = x.double() @ w.double().t()
+    got32 = ops.skinny_gemm(dev(x), dev(w), torch.float32).cpu()
+    assert (got32.double() - want).abs().max() <= 2e-5 * max(1.0, math.sqrt(K))    # float32 sums of exact products
+    got16 = ops.skinny_gemm(dev(x), dev(w)).cpu()
+    assert bool(((got16.double() - want).abs() <= 2.0 ** -8 * want.abs() + 1e-4).all())
+    assert torch.equal(ops.linear(dev(x), dev(w)).cpu(), got16)                   # `linear` takes this path
+    one = ops.skinny_gemm(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w), torch.float32).cpu()
+    assert torch.equal(one[0], got32[M // 2])                                     # a row ignores its neighbours
+
+
+@pytest.mark.parametrize("I,K,M", [(8, 16, 2), (176, 80, 7), (8192, 2048, 8)])
+def test_skinny_product_with_gating_and_interleaved_gating_kernel(I, K, M):
+    from rust_llm_inference_server_b200 import ops
+    torch.manual_seed(I)
+    x = torch.randn(M, K).bfloat16()
+    g, u = (torch.randn(I, K) * 0.1).bfloat16(), (torch.randn(I, K) * 0.1).bfloat16()
+    w = torch.stack([g.view(-1, 4, K), u.view(-1, 4, K)], dim=1).reshape(2 * I, K).contiguous()
+    gate, up = x.double() @ g.double().t(), x.double() @ u.double().t()
+    want = torch.nn.functional.silu(gate) * up
+    got = ops.skinny_gemm(dev(x), dev(w), swiglu4=True).cpu()
+    assert got.shape == (M, I)
+    assert bool(((got.double() - want).abs() <= 2.0 ** -7 * want.abs() + 1e-3).all())
+    # the two-kernel path of longer batches: product, then the gating kernel on the interleaved layout
+    gu = (x.double() @ w.double().t()).float()
+    for dtype in DT:
+        out = torch.empty(M, I, dtype=dtype, device="cuda")
+        ops.swiglu(dev(gu.to(dtype)), out, interleave=4)
+        gq, uq = gu.to(dtype).double().view(M, -1, 2, 4)[:, :, 0].reshape(M, I), gu.to(dtype).double().view(M, -1, 2, 4)[:, :, 1].reshape(M, I)
+        w2 = torch.nn.functional.silu(gq) * uq
+        assert bool(((out.double().cpu() - w2).abs() <= 2.0 ** -7 * w2.abs() + 1e-5).all())
+
+
 def cache_from(k, v, page_size, n_pages, seed=0):
     """Scatters contiguous k, v [(requests) x (len, nkv, d)] into a paged cache with shuffled,
     interleaved pages; returns caches [pages, nkv, page, d] and the block tables."""
