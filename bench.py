@@ -277,14 +277,19 @@ def main() -> int:
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src}
 
     # ---- end to end through the Python entry point ----
-    prompts = [rng.integers(0, V, size=context - total - 1).tolist() for _ in range(B)]
-    sp = SamplingParams(max_tokens=total + 1, ignore_eos=True)
+    # The prompts finish their prefill in different steps (the token budget cuts them), so the
+    # requests do not decode in lockstep; each gets enough output that all B decode together for
+    # warmup + steps steps, the last of which sees a context of about `context` tokens.
+    stagger = B * (context // 2048 + 1)
+    e2e_out = total + stagger + 8
+    prompts = [rng.integers(0, V, size=context - e2e_out - 1).tolist() for _ in range(B)]
+    sp = SamplingParams(max_tokens=e2e_out, ignore_eos=True)
     eng = llm.engine
-    h2d0 = d2h0 = 0
+    h2d0 = d2h0 = h2d1 = d2h1 = 0
     t0 = t1 = None
     n_decode = 0
     for ev in llm.stream(prompts, sp):
-        if not ev.all_decoding:
+        if not (ev.all_decoding and ev.n_seqs == B) or t1 is not None:
             continue
         n_decode += 1
         if n_decode == args.warmup:

@@ -59,12 +59,17 @@ class StepContext:
         self.max_decode_ctx = 0
         self.n_prefill_tokens = 0
         self.prefill_rows = None                  # int32: rows of the tokens of longer entries
+        self.n_prefill_tiles = 0
+        self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token), 64 tokens a tile
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self._runner.workspace(name, shape, dtype)
 
 
 class ModelRunner:
+    PREFILL_TILE = 64           # query tokens per CTA of the prefill attention kernel
+    GRAPH_AFTER_STEPS = 2       # eager steps of a decode shape before its graph is captured
+
     def __init__(self, model, cache_manager, storage, max_seq_len: int):
         self.model = model
         self.cache = cache_manager
@@ -83,7 +88,7 @@ class ModelRunner:
         # a buffer they point into is replaced by a larger one
         self.use_graphs = True
         self._graphs: dict = {}
-        self._graph_seen: set = set()
+        self._graph_seen: dict = {}     # key -> times seen before its capture
         self._graph_pool = None
         self._upload_done = None
         self._graph_launches = 0
@@ -167,10 +172,13 @@ class ModelRunner:
                 pf_rows.extend(range(k, k + n))
             k += n
         Bd, Tp = len(dec_rows), len(pf_rows)
+        pf_tiles = [(b, t0) for b, n in enumerate(lens) if n > 1 for t0 in range(0, n, self.PREFILL_TILE)]
+        Nt = len(pf_tiles)
         o_dr = o_rows + _align4(max(W, 1))
         o_ds = o_dr + _align4(max(Bd, 1))
         o_pr = o_ds + _align4(max(Bd, 1))
-        o_bt = o_pr + _align4(max(Tp if Bd else 0, 1))
+        o_pt = o_pr + _align4(max(Tp if Bd else 0, 1))
+        o_bt = o_pt + _align4(max(2 * Nt, 1))
         total = o_bt + G * B * mb
         host, dev = self._meta(total)
         if self._upload_done is not None:
@@ -193,6 +201,8 @@ class ModelRunner:
             raise StepError(str(err)) from None
         if W:
             h[o_rows:o_rows + W] = want_rows
+        if Nt:
+            h[o_pt:o_pt + 2 * Nt] = np.asarray(pf_tiles, dtype=np.int32).reshape(-1)
         if Bd:
             h[o_dr:o_dr + Bd] = dec_rows
             h[o_ds:o_ds + Bd] = dec_seqs
@@ -223,11 +233,14 @@ class ModelRunner:
         st.all_decode = st.max_q_len == 1
         st.h2d_bytes = total * 4
         st.n_decode = Bd
+        st.n_prefill_tokens = Tp
+        st.n_prefill_tiles = Nt
+        if Nt:
+            st.prefill_tiles = dev[o_pt:o_pt + 2 * Nt].view(Nt, 2)
         if Bd:
             st.dec_rows = dev[o_dr:o_dr + Bd]
             st.dec_seqs = dev[o_ds:o_ds + Bd]
             st.max_decode_ctx = max(starts[b] + 1 for b in dec_seqs)
-            st.n_prefill_tokens = Tp
             st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
         return st
 
@@ -255,9 +268,12 @@ class ModelRunner:
             return self._forward_eager(st)
         entry = self._graphs.get(key)
         if entry is None:
-            if key not in self._graph_seen:
-                # first sight: run eagerly, which also sizes every scratch buffer for this shape
-                self._graph_seen.add(key)
+            # The first steps of a shape run eagerly (which also sizes every scratch buffer for it);
+            # a capture costs tens of milliseconds, so shapes that only pass by (a batch that is
+            # shrinking as requests finish) never pay it.
+            seen = self._graph_seen.get(key, 0)
+            if seen < self.GRAPH_AFTER_STEPS:
+                self._graph_seen[key] = seen + 1
                 return self._forward_eager(st)
             before = ops.launch_count
             graph = torch.cuda.CUDAGraph()
@@ -268,8 +284,6 @@ class ModelRunner:
                 logits = self._forward_eager(st)
             n = ops.launch_count - before
             ops.launch_count = before           # capturing launches nothing
-            if key not in self._graph_seen or not self.use_graphs:
-                return self._forward_eager(st)
             entry = (graph, logits, n)
             self._graphs[key] = entry
         graph, logits, n = entry

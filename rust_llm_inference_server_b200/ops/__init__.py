@@ -259,29 +259,65 @@ def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, blo
     return out
 
 
+def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,
+                      n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                      window: int = 0) -> torch.Tensor:
+    """Causal flash attention of portions of prompts over the paged cache (bfloat16, head sizes 64
+    and 128).  tiles int32 [n, 2] = (batch entry, first token of the 64-token tile within the
+    entry's portion); cu_seqlens int32 [B + 1] = rows of the entries' first tokens."""
+    _req(q, "q", torch.bfloat16, (None, n_heads * head_dim))
+    _req(out, "out", torch.bfloat16, tuple(q.shape))
+    _req(k_cache, "k_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    _req(v_cache, "v_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    _req(tiles, "tiles", torch.int32, (None, 2))
+    _req(cu_seqlens, "cu_seqlens", torch.int32, (None,))
+    _req(ctx_lens, "ctx_lens", torch.int32, (None,))
+    _req(block_tables, "block_tables", torch.int32, (None, None))
+    if head_dim not in (64, 128) or n_heads % n_kv_heads:
+        raise KernelError(f"prefill attention: head size {head_dim} is not taken (64 and 128 are)")
+    check(lib().rlis_attention_prefill(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
+        tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),
+        block_tables.shape[1], n_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
+        _code(q.dtype), _stream()), "attention_prefill")
+    _count()
+    return out
+
+
 def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_heads: int,
               head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
     """Attention of every token of the step over its request's cached keys, by the kernels that
-    fit the step: single decoded tokens (bfloat16) go to the split decode kernel, everything else
-    to the kernel for any query length.  The choice never changes the result beyond rounding."""
-    fast_decode = (q.dtype == torch.bfloat16 and step.n_decode > 0 and n_heads // n_kv_heads <= 8
-                   and head_dim % 8 == 0)
-    if not fast_decode:
-        return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
-                                 step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size,
-                                 scale, window)
-    splits = decode_splits(step.n_decode, n_kv_heads, step.max_decode_ctx)
-    scratch = None
-    if splits > 1:
-        scratch = step.buffer("attn_partial", (step.n_decode * n_heads * splits * (head_dim + 2),), torch.float32)
-    attention_decode(q, k_cache, v_cache, out, step.dec_rows, step.dec_seqs, step.ctx_lens,
-                     step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size, scale, window,
-                     splits, scratch)
-    if step.n_prefill_tokens > 0:
-        attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions,
-                          step.block_tables[group], n_heads, n_kv_heads, head_dim, page_size, scale,
-                          window, token_rows=step.prefill_rows)
-    return out
+    fit the step.  bfloat16: single decoded tokens go to the split decode kernel, portions of
+    prompts to the flash kernel (head sizes 64 and 128); everything else, and all of float32, to
+    the kernel for any query length.  The choice never changes the result beyond rounding."""
+    tables = step.block_tables[group]
+    bf = q.dtype == torch.bfloat16
+    dec_fast = bf and step.n_decode > 0 and n_heads // n_kv_heads <= 8 and head_dim % 8 == 0
+    pf_fast = bf and step.n_prefill_tiles > 0 and head_dim in (64, 128)
+    if dec_fast:
+        splits = decode_splits(step.n_decode, n_kv_heads, step.max_decode_ctx)
+        scratch = None
+        if splits > 1:
+            scratch = step.buffer("attn_partial", (step.n_decode * n_heads * splits * (head_dim + 2),), torch.float32)
+        attention_decode(q, k_cache, v_cache, out, step.dec_rows, step.dec_seqs, step.ctx_lens, tables,
+                         n_heads, n_kv_heads, head_dim, page_size, scale, window, splits, scratch)
+    if pf_fast:
+        attention_prefill(q, k_cache, v_cache, out, step.prefill_tiles, step.cu_seqlens, step.ctx_lens,
+                          tables, n_heads, n_kv_heads, head_dim, page_size, scale, window)
+    if dec_fast and pf_fast:
+        return out
+    if not dec_fast and not pf_fast:
+        rows = None                                   # every token of the step
+    elif dec_fast:
+        if step.n_prefill_tokens == 0:
+            return out
+        rows = step.prefill_rows                      # the portions only
+    else:
+        if step.n_decode == 0:
+            return out
+        rows = step.dec_rows                          # the single tokens only
+    return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions, tables,
+                             n_heads, n_kv_heads, head_dim, page_size, scale, window, token_rows=rows)
 
 
 def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -297,6 +297,42 @@ def test_decode_attention_split_over_the_context(geom, ps, splits):
     assert err <= 2e-2, err
 
 
+@pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((6, 3, 128), 16), ((4, 4, 64), 8), ((5, 1, 128), 32)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_prefill_flash_attention_over_pages(geom, ps, window):
+    """Portions of prompts of many lengths (one token short of a tile, exactly a tile, across
+    tiles), starting at position 0 and deep in a context, against plain attention."""
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d = geom
+    lens = [300, 64, 65, 130, 700, 2, 191]
+    q_lens = [300, 64, 2, 127, 129, 2, 63]
+    q, kc, vc, tables, sot, pos, want = attention_case(geom, lens, q_lens, ps, torch.bfloat16, window=window, seed=d + ps)
+    tiles = torch.tensor([(b, t0) for b, n in enumerate(q_lens) for t0 in range(0, n, 64)], dtype=torch.int32)
+    cu = torch.tensor(np.cumsum([0] + q_lens), dtype=torch.int32)
+    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+    ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)),
+                          dev(tables), nh, nkv, d, ps, 1 / math.sqrt(d), window or 0)
+    err = (out.float().cpu().view(-1, nh, d) - want).abs().max()
+    assert err <= 2.5e-2, err
+
+
+def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
+    from rust_llm_inference_server_b200 import ops
+    geom, ps = (8, 2, 64), 16
+    n, m = 1000, 200           # the last 200 tokens are queries
+    cu = torch.tensor([0, m], dtype=torch.int32)
+    tiles = torch.tensor([(0, t0) for t0 in range(0, m, 64)], dtype=torch.int32)
+    for qi, key, seen in ((0, 3, True), (0, 800, True), (0, 801, False), (150, 950, True), (150, 951, False),
+                          (199, 999, True), (64, 864, True), (63, 864, False), (100, 15, True), (100, 16, True)):
+        q, kc, vc, tables, sot, pos, want = attention_case(geom, [n], [m], ps, torch.bfloat16, seed=key, spike=(0, qi, key))
+        out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+        ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu), dev(torch.tensor([n], dtype=torch.int32)),
+                              dev(tables), 8, 2, 64, ps, 0.125, 0)
+        got = out.float().cpu().view(m, 8, 64)
+        assert (got - want).abs().max() <= 3e-2
+        assert ((got[qi] - 7.0).abs().max() < 0.05) == seen, (qi, key)
+
+
 def test_decode_attention_far_key_and_window():
     from rust_llm_inference_server_b200 import ops
     geom, ps = (8, 2, 64), 16

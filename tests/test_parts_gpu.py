@@ -44,8 +44,12 @@ class FakeStep:
         self.dec_rows = i32([self.q_starts[b] for b in dec]) if dec else None
         self.max_decode_ctx = max([starts[b] + 1 for b in dec], default=0)
         rows = [r for b, n in enumerate(lens) if n > 1 for r in range(self.q_starts[b], self.q_starts[b] + n)]
-        self.n_prefill_tokens = len(rows) if dec else 0
+        self.n_prefill_tokens = len(rows)
         self.prefill_rows = i32(rows) if (dec and rows) else None
+        tiles = [(b, t0) for b, n in enumerate(lens) if n > 1 for t0 in range(0, n, 64)]
+        self.n_prefill_tiles = len(tiles)
+        self.prefill_tiles = i32(tiles) if tiles else None
+        self.cu_seqlens = i32(self.q_starts + [self.n_tokens])
         self._bufs = {}
 
     def buffer(self, name, shape, dtype):
