@@ -63,6 +63,68 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     }
 }
 
+// The same with 16-byte accesses: a thread takes one vector of the first half of a head and the
+// matching vector of the second half (head sizes whose half is a multiple of the vector length).
+template <typename T>
+__global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                      const int* __restrict__ positions, const int* __restrict__ slots,
+                                      const float* __restrict__ inv_freq, int nh, int nkv, int d,
+                                      int page_size) {
+    constexpr int VN = Vec16<T>::N;
+    extern __shared__ float cs[];
+    const int t = blockIdx.x;
+    const int half = d >> 1;
+    float* cc = cs;
+    float* sn = cs + half;
+    const float pos = (float)positions[t];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float s_ = 0.f, c_ = 1.f;
+        if (inv_freq != nullptr) sincosf(pos * inv_freq[j], &s_, &c_);
+        cc[j] = c_;
+        sn[j] = s_;
+    }
+    __syncthreads();
+    const T* x = qkv + (size_t)t * (nh + 2 * nkv) * d;
+    const int slot = slots != nullptr ? slots[t] : -1;
+    const long long page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? slot % page_size : 0;
+    const int cph = half / VN;                       // vectors per half head
+    const int items = (nh + 2 * nkv) * cph;
+    for (int idx = threadIdx.x; idx < items; idx += blockDim.x) {
+        const int head = idx / cph, j0 = (idx - head * cph) * VN;
+        const uint4 r1 = *reinterpret_cast<const uint4*>(x + head * d + j0);
+        const uint4 r2 = *reinterpret_cast<const uint4*>(x + head * d + half + j0);
+        T* dst;
+        if (head < nh) {
+            dst = q_out + ((size_t)t * nh + head) * d;
+        } else if (slot < 0) {
+            continue;
+        } else if (head < nh + nkv) {
+            dst = k_cache + (((size_t)page * nkv + (head - nh)) * page_size + off) * d;
+        } else {
+            dst = v_cache + (((size_t)page * nkv + (head - nh - nkv)) * page_size + off) * d;
+            *reinterpret_cast<uint4*>(dst + j0) = r1;
+            *reinterpret_cast<uint4*>(dst + half + j0) = r2;
+            continue;
+        }
+        float a[VN], b[VN];
+        load16<T>(reinterpret_cast<const T*>(&r1), a);
+        load16<T>(reinterpret_cast<const T*>(&r2), b);
+        uint4 o1, o2;
+        T* p1 = reinterpret_cast<T*>(&o1);
+        T* p2 = reinterpret_cast<T*>(&o2);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+            const float c_ = cc[j0 + e], s_ = sn[j0 + e];
+            p1[e] = from_f<T>(a[e] * c_ - b[e] * s_);
+            p2[e] = from_f<T>(b[e] * c_ + a[e] * s_);
+        }
+        *reinterpret_cast<uint4*>(dst + j0) = o1;
+        *reinterpret_cast<uint4*>(dst + half + j0) = o2;
+    }
+}
+
 extern "C" int rlis_rope_cache(const void* qkv, void* q_out, void* k_cache, void* v_cache,
                                const int* positions, const int* slots, const float* inv_freq,
                                int n_tokens, int nh, int nkv, int d, int page_size, int dtype,
@@ -71,6 +133,20 @@ extern "C" int rlis_rope_cache(const void* qkv, void* q_out, void* k_cache, void
     if (d <= 0 || (d & 1)) return RLIS_ERR_UNSUPPORTED;
     const int threads = 256;
     const size_t smem = (size_t)d * sizeof(float);
+    const int vn = dtype == RLIS_F32 ? 4 : 8;
+    if ((d / 2) % vn == 0 && (dtype == RLIS_F32 || dtype == RLIS_BF16)) {
+        const int items = (nh + 2 * nkv) * (d / 2 / vn);
+        const int th = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        if (dtype == RLIS_F32)
+            rope_cache_vec_kernel<float><<<n_tokens, th, smem, stream>>>(
+                (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots, inv_freq,
+                nh, nkv, d, page_size);
+        else
+            rope_cache_vec_kernel<bf16><<<n_tokens, th, smem, stream>>>(
+                (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, inv_freq,
+                nh, nkv, d, page_size);
+        return RLIS_LAUNCH_CHECK();
+    }
     if (dtype == RLIS_F32)
         rope_cache_kernel<float><<<n_tokens, threads, smem, stream>>>(
             (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots,
