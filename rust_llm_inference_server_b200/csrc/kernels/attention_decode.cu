@@ -32,6 +32,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int d, int page_size,
     float scale, int window, int splits) {
+    pdl_wait();
     extern __shared__ __align__(16) float smem[];
     // smem: q [NREP][d] | p per warp [DEC_WARPS][32][NREP] | merge area
     float* qs = smem;
@@ -190,6 +191,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
             }
         }
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // Tensor-core version for head sizes 64 and 128 (groups of up to 8 query heads).  The CUDA-core
@@ -208,7 +210,9 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
-    float scale, int window, int splits) {
+    float scale, int window, int splits, int* __restrict__ tickets) {
+    pdl_wait();
+    __shared__ int s_last;
     constexpr int STRIDE = D + 8;            // elements per padded row
     constexpr int KS = D / 16;               // k-steps of Q K^T
     constexpr int ND = D / 8;                // n-tiles of P V
@@ -245,22 +249,32 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         }
     }
 
+    // Address arithmetic of the copies is kept short: it runs 2 * CPR times per block and lane and
+    // would otherwise outweigh the tensor work.  A page size that is a power of two (the usual
+    // case) turns the division into a shift.
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    const size_t page_stride = (size_t)nkv * head_stride;
+    const bf16* kbase = k_cache + (size_t)kvh * head_stride;
+    const bf16* vbase = v_cache + (size_t)kvh * head_stride;
+    const int key_in0 = lane / CPR, c16 = lane % CPR;       // chunk i of a lane: key_in0 + i * (32 / CPR)
+    const uint32_t sm_off0 = (uint32_t)(key_in0 * STRIDE + c16 * 8);
     auto issue = [&](int blk, int stage) {
         bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
         bf16* vs_ = ks_ + TILE;
 #pragma unroll
         for (int i = 0; i < CPR; ++i) {               // 32 * CPR chunks, 32 lanes
-            const int chunk = i * 32 + lane;
-            const int key_in = chunk / CPR, c16 = chunk % CPR;
+            const int key_in = key_in0 + i * (32 / CPR);
             const int key = (blk << 5) + key_in;
             const bool valid = key >= lo_all && key < ctx;
             size_t off = 0;
             if (valid) {
-                const int page = table[key / page_size];
-                off = ((size_t)page * nkv + kvh) * head_stride + (size_t)(key % page_size) * D + c16 * 8;
+                const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+                off = (size_t)table[pi] * page_stride + (uint32_t)(in_page * D + c16 * 8);
             }
-            cp_async16(ks_ + key_in * STRIDE + c16 * 8, k_cache + off, valid);
-            cp_async16(vs_ + key_in * STRIDE + c16 * 8, v_cache + off, valid);
+            const uint32_t so = sm_off0 + (uint32_t)(i * (32 / CPR) * STRIDE);
+            cp_async16(ks_ + so, kbase + off, valid);
+            cp_async16(vs_ + so, vbase + off, valid);
         }
         cp_async_commit();
     };
@@ -398,7 +412,40 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             }
         }
     }
+    if (splits > 1 && tickets != nullptr) {
+        // The CTA that takes the last ticket of its (request, kv head) merges the splits, in split
+        // order; nobody waits for anybody.  The counter is zero again when the launch ends.
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(&tickets[bi * nkv + kvh], 1) == splits - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int i = threadIdx.x; i < nrep * D; i += DEC_THREADS) {
+                const int h = i / D, j = i - h * D;
+                const int head = kvh * nrep + h;
+                const float* pr = partial + ((size_t)bi * nh + head) * splits * (D + 2);
+                float big = -INFINITY;
+                for (int sp = 0; sp < splits; ++sp) big = fmaxf(big, __ldcg(pr + (size_t)sp * (D + 2) + D));
+                float a = 0.f, lsum = 0.f;
+                for (int sp = 0; sp < splits; ++sp) {
+                    const float* r = pr + (size_t)sp * (D + 2);
+                    const float mw = __ldcg(r + D);
+                    const float wgt = mw == -INFINITY ? 0.f : expf(mw - big);
+                    a += __ldcg(r + j) * wgt;
+                    lsum += __ldcg(r + D + 1) * wgt;
+                }
+                out[((size_t)row * nh + head) * D + j] = from_f<bf16>(a / lsum);
+            }
+            if (threadIdx.x == 0) tickets[bi * nkv + kvh] = 0;
+        }
+    }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
+
+// Ticket counters of the fused merge, part of the library image, zero between launches.
+constexpr int kMaxTickets = 65536;
+__device__ int g_decode_tickets[kMaxTickets];
 
 template <int D> constexpr size_t decode_mma_smem_bytes() {
     return (size_t)DEC_WARPS * 4 * 32 * (D + 8) * sizeof(bf16);
@@ -409,6 +456,7 @@ template <int D> constexpr size_t decode_mma_smem_bytes() {
 __global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                            const int* __restrict__ dec_rows, int nh, int d,
                                            int splits) {
+    pdl_wait();
     const int bi = blockIdx.y, head = blockIdx.x;
     const float* pr = partial + ((size_t)bi * nh + head) * splits * (d + 2);
     float big = -INFINITY;
@@ -424,6 +472,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf
         }
         out[((size_t)row * nh + head) * d + j] = from_f<bf16>(a / lsum);
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 size_t decode_smem_bytes(int nrep, int d) {
@@ -454,7 +503,21 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
     dim3 grid(nkv, n_decode, splits);
     const size_t smem = decode_smem_bytes(nrep, d);
     bool launched = false;
+    bool merged = false;
     if (d == 64 || d == 128) {
+        int* tickets = nullptr;
+        if (splits > 1 && (long long)n_decode * nkv <= kMaxTickets) {
+            static int* ticket_ptr[64] = {nullptr};
+            int dev = -1;
+            if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+                if (ticket_ptr[dev] == nullptr) {
+                    int* p = nullptr;
+                    if (cudaGetSymbolAddress((void**)&p, g_decode_tickets) == cudaSuccess) ticket_ptr[dev] = p;
+                }
+                tickets = ticket_ptr[dev];
+            }
+        }
+        merged = tickets != nullptr;
         static bool attr_done[2] = {false, false};
         if (d == 64) {
             if (!attr_done[0]) {
@@ -462,23 +525,23 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
                                      (int)decode_mma_smem_bytes<64>());
                 attr_done[0] = true;
             }
-            attn_decode_mma_kernel<64><<<grid, DEC_THREADS, decode_mma_smem_bytes<64>(), stream>>>(
+            rlis_launch(attn_decode_mma_kernel<64>, grid, DEC_THREADS, decode_mma_smem_bytes<64>(), stream, 
                 (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
-                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits);
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets);
         } else {
             if (!attr_done[1]) {
                 cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)decode_mma_smem_bytes<128>());
                 attr_done[1] = true;
             }
-            attn_decode_mma_kernel<128><<<grid, DEC_THREADS, decode_mma_smem_bytes<128>(), stream>>>(
+            rlis_launch(attn_decode_mma_kernel<128>, grid, DEC_THREADS, decode_mma_smem_bytes<128>(), stream, 
                 (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
-                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits);
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets);
         }
         launched = true;
     }
 #define LAUNCH(N)                                                                                   \
-    attn_decode_kernel<N><<<grid, DEC_THREADS, smem, stream>>>(                                     \
+    rlis_launch(attn_decode_kernel<N>, grid, DEC_THREADS, smem, stream,                                      \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows,  \
         dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, d, page_size, scale, window, splits)
     if (!launched) switch (nrep) {
@@ -494,9 +557,9 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
     }
 #undef LAUNCH
     int err = RLIS_LAUNCH_CHECK();
-    if (err != 0 || splits == 1) return err;
+    if (err != 0 || splits == 1 || merged) return err;
     const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
-    attn_decode_combine_kernel<<<dim3(nh, n_decode), threads, 0, stream>>>(partial, (bf16*)out, dec_rows, nh, d, splits);
+    rlis_launch(attn_decode_combine_kernel, dim3(nh, n_decode), threads, 0, stream, partial, (bf16*)out, dec_rows, nh, d, splits);
     return RLIS_LAUNCH_CHECK();
 }
 

@@ -24,6 +24,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
     T* __restrict__ out, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
     const int* __restrict__ block_tables, const int* __restrict__ token_rows, int max_blocks,
     int n_rows, int nh, int nkv, int d, int page_size, float scale, int window) {
+    pdl_wait();
     extern __shared__ float qs_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gw = blockIdx.x * WARPS + warp;
@@ -95,6 +96,7 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
         const int dim = lane + 32 * i;
         if (dim < d) orow[dim] = from_f<T>(acc[i] * inv_l);
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 }  // namespace
 
@@ -111,11 +113,11 @@ extern "C" int rlis_attention_generic(const void* q, const void* k_cache, const 
     const unsigned blocks = (unsigned)((n_rows + WARPS - 1) / WARPS);
     const size_t smem = (size_t)WARPS * d * sizeof(float);
     if (dtype == RLIS_F32)
-        attn_generic_kernel<float><<<blocks, WARPS * 32, smem, stream>>>(
+        rlis_launch(attn_generic_kernel<float>, blocks, WARPS * 32, smem, stream, 
             (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, seq_of_token,
             positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
     else if (dtype == RLIS_BF16)
-        attn_generic_kernel<bf16><<<blocks, WARPS * 32, smem, stream>>>(
+        rlis_launch(attn_generic_kernel<bf16>, blocks, WARPS * 32, smem, stream, 
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, seq_of_token,
             positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, page_size, scale, window);
     else

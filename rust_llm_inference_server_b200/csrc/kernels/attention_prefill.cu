@@ -30,6 +30,7 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
     bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ block_tables, int max_blocks, int nh,
     int nkv, int page_size, float scale, int window) {
+    pdl_wait();
     constexpr int STRIDE = D + 8;
     constexpr int KS = D / 16;
     constexpr int ND = D / 8;
@@ -76,22 +77,30 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
     const int k_lo = window > 0 ? max(0, start_pos + t0 - window + 1) : 0;
     const int kt0 = k_lo / PF_BN, kt1 = (k_hi + PF_BN - 1) / PF_BN;
 
+    // (short address arithmetic: a power-of-two page size turns the division into a shift)
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    const size_t page_stride = (size_t)nkv * head_stride;
+    const bf16* kbase = k_cache + (size_t)kvh * head_stride;
+    const bf16* vbase = v_cache + (size_t)kvh * head_stride;
+    const int key_in0 = threadIdx.x / CPR, c16 = threadIdx.x % CPR;
+    constexpr int KEYS_PER_IT = PF_THREADS / CPR;
+    const uint32_t sm_off0 = (uint32_t)(key_in0 * STRIDE + c16 * 8);
     auto issue = [&](int kt, int stage) {
         bf16* ks_ = sbase + (size_t)stage * 2 * TILE;
         bf16* vs_ = ks_ + TILE;
 #pragma unroll
         for (int i = 0; i < (PF_BN * CPR) / PF_THREADS; ++i) {
-            const int chunk = i * PF_THREADS + threadIdx.x;
-            const int key_in = chunk / CPR, c16 = chunk % CPR;
-            const int key = kt * PF_BN + key_in;
+            const int key = kt * PF_BN + key_in0 + i * KEYS_PER_IT;
             const bool valid = key < k_hi && key >= k_lo;
             size_t off = 0;
             if (valid) {
-                const int page = table[key / page_size];
-                off = ((size_t)page * nkv + kvh) * head_stride + (size_t)(key % page_size) * D + c16 * 8;
+                const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+                off = (size_t)table[pi] * page_stride + (uint32_t)(in_page * D + c16 * 8);
             }
-            cp_async16(ks_ + key_in * STRIDE + c16 * 8, k_cache + off, valid);
-            cp_async16(vs_ + key_in * STRIDE + c16 * 8, v_cache + off, valid);
+            const uint32_t so = sm_off0 + (uint32_t)(i * KEYS_PER_IT * STRIDE);
+            cp_async16(ks_ + so, kbase + off, valid);
+            cp_async16(vs_ + so, vbase + off, valid);
         }
         cp_async_commit();
     };
@@ -211,6 +220,7 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
         for (int nd = 0; nd < ND; ++nd)
             *reinterpret_cast<uint32_t*>(o + nd * 8 + 2 * c) = pack_bf16(oacc[nd][2] * inv1, oacc[nd][3] * inv1);
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 template <int D> constexpr size_t prefill_smem_bytes() {
@@ -237,11 +247,11 @@ extern "C" int rlis_attention_prefill(const void* q, const void* k_cache, const 
         attr_done = true;
     }
     if (d == 64)
-        attn_prefill_mma_kernel<64><<<grid, PF_THREADS, prefill_smem_bytes<64>(), stream>>>(
+        rlis_launch(attn_prefill_mma_kernel<64>, grid, PF_THREADS, prefill_smem_bytes<64>(), stream, 
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tiles, cu_seqlens, ctx_lens,
             block_tables, max_blocks, nh, nkv, page_size, scale, window);
     else
-        attn_prefill_mma_kernel<128><<<grid, PF_THREADS, prefill_smem_bytes<128>(), stream>>>(
+        rlis_launch(attn_prefill_mma_kernel<128>, grid, PF_THREADS, prefill_smem_bytes<128>(), stream, 
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tiles, cu_seqlens, ctx_lens,
             block_tables, max_blocks, nh, nkv, page_size, scale, window);
     return RLIS_LAUNCH_CHECK();

@@ -73,3 +73,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 #define RLIS_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+// ---- programmatic dependent launch --------------------------------------------------------
+// Every kernel of this library calls pdl_wait() before it touches anything an earlier kernel of
+// the stream may write (or may still read), and pdl_trigger() as its CTAs finish.  Launched with
+// the programmatic-serialization attribute, the next kernel's CTAs are then launched while this
+// kernel's last CTAs drain, and run their prologue (the first weight vectors of a weight-streaming
+// product) before they wait; without the attribute both calls do nothing.  Before pdl_wait() a
+// kernel may read only memory that no kernel of the step writes: weights and index arrays.
+// (Triggering at the top of a kernel instead lets kernels pile up several deep, each holding SM
+// slots while it waits; the decode step ran a fifth slower that way.)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_rlis_pdl;   // 0 (default): plain launches; see rlis_set_pdl in pdl.cu
+
+template <typename... KArgs, typename... Args>
+static inline void rlis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rlis_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

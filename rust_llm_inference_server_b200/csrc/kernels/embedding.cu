@@ -6,6 +6,7 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -15,6 +16,7 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     }
     const T* row = table + (size_t)id * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f<T>(row[i]);
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_embedding(const int* ids, const void* table, float* out, int n_tokens,
@@ -22,9 +24,9 @@ extern "C" int rlis_embedding(const int* ids, const void* table, float* out, int
     if (n_tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == RLIS_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        rlis_launch(embedding_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
     else if (dtype == RLIS_BF16)
-        embedding_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
+        rlis_launch(embedding_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

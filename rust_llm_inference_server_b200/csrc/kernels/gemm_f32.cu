@@ -10,6 +10,7 @@ constexpr int BM = 64, BN = 64, BK = 16;
 __global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__ A,
                                                        const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K) {
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -52,6 +53,7 @@ __global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__
             if (gn < N) C[(size_t)gm * N + gn] = acc[i][j];
         }
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 }  // namespace
 
@@ -60,6 +62,6 @@ extern "C" int rlis_gemm_f32_nt(const float* A, const float* W, float* C, int M,
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
-    sgemm_nt_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K);
+    rlis_launch(sgemm_nt_kernel, grid, 256, 0, stream, A, W, C, M, N, K);
     return RLIS_LAUNCH_CHECK();
 }

@@ -11,6 +11,7 @@ __global__ __launch_bounds__(NLL_THREADS) void nll_rows_kernel(const float* __re
                                                                const int* __restrict__ targets,
                                                                float* __restrict__ nll, int vocab,
                                                                long long row_stride) {
+    pdl_wait();
     __shared__ float scratch[33];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     float mx = -INFINITY;
@@ -33,6 +34,7 @@ __global__ __launch_bounds__(NLL_THREADS) void nll_rows_kernel(const float* __re
         const int t = targets[blockIdx.x];
         nll[blockIdx.x] = (t >= 0 && t < vocab) ? logf(s) + mx - row[t] : NAN;
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 }  // namespace
 
@@ -40,6 +42,6 @@ extern "C" int rlis_nll_rows(const float* logits, const int* targets, float* nll
                              long long row_stride, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return RLIS_ERR_UNSUPPORTED;
-    nll_rows_kernel<<<rows, NLL_THREADS, 0, stream>>>(logits, targets, nll, vocab, row_stride);
+    rlis_launch(nll_rows_kernel, rows, NLL_THREADS, 0, stream, logits, targets, nll, vocab, row_stride);
     return RLIS_LAUNCH_CHECK();
 }

@@ -15,6 +15,7 @@ template <typename T>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ rows, int hidden, float eps) {
+    pdl_wait();
     __shared__ float scratch[33];
     const size_t obase = (size_t)blockIdx.x * hidden;
     if (rows != nullptr) {
@@ -50,6 +51,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ 
     const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         out[base + i] = from_f<T>(resid[base + i] * rstd * w[i]);
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // The same for widths that are multiples of 4: 16-byte accesses, and the row is kept
@@ -79,6 +81,7 @@ template <typename T>
 __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                     const float* __restrict__ w, T* __restrict__ out,
                                     const int* __restrict__ rows, int hidden, float eps) {
+    pdl_wait();
     __shared__ float scratch[33];
     constexpr int MAXV = 4;
     const size_t obase = (size_t)blockIdx.x * hidden;
@@ -115,6 +118,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restri
                              make_float4(x.x * rstd * ww.x, x.y * rstd * ww.y, x.z * rstd * ww.z, x.w * rstd * ww.w));
         }
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_rmsnorm(float* resid, const void* delta, const float* w, void* out,
@@ -124,17 +128,17 @@ extern "C" int rlis_rmsnorm(float* resid, const void* delta, const float* w, voi
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if ((hidden & 3) == 0 && hidden <= threads * 16) {
         if (dtype == RLIS_F32)
-            rmsnorm_vec4_kernel<float><<<n_tokens, threads, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+            rlis_launch(rmsnorm_vec4_kernel<float>, n_tokens, threads, 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
         else if (dtype == RLIS_BF16)
-            rmsnorm_vec4_kernel<bf16><<<n_tokens, threads, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+            rlis_launch(rmsnorm_vec4_kernel<bf16>, n_tokens, threads, 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
         else
             return RLIS_ERR_UNSUPPORTED;
         return RLIS_LAUNCH_CHECK();
     }
     if (dtype == RLIS_F32)
-        rmsnorm_kernel<float><<<n_tokens, threads, 0, stream>>>(resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
+        rlis_launch(rmsnorm_kernel<float>, n_tokens, threads, 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);
     else if (dtype == RLIS_BF16)
-        rmsnorm_kernel<bf16><<<n_tokens, threads, 0, stream>>>(resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
+        rlis_launch(rmsnorm_kernel<bf16>, n_tokens, threads, 0, stream, resid, (const bf16*)delta, w, (bf16*)out, rows, hidden, eps);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -15,6 +15,7 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ positions, const int* __restrict__ slots,
                                   const float* __restrict__ inv_freq, int nh, int nkv, int d,
                                   int page_size) {
+    pdl_wait();
     extern __shared__ float cs[];  // cos[half], sin[half]
     const int t = blockIdx.x;
     const int half = d >> 1;
@@ -61,6 +62,7 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
             }
         }
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // The same with 16-byte accesses: a thread takes one vector of the first half of a head and the
@@ -71,6 +73,7 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
                                       const int* __restrict__ positions, const int* __restrict__ slots,
                                       const float* __restrict__ inv_freq, int nh, int nkv, int d,
                                       int page_size) {
+    pdl_wait();
     constexpr int VN = Vec16<T>::N;
     extern __shared__ float cs[];
     const int t = blockIdx.x;
@@ -123,6 +126,7 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
         *reinterpret_cast<uint4*>(dst + j0) = o1;
         *reinterpret_cast<uint4*>(dst + half + j0) = o2;
     }
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_rope_cache(const void* qkv, void* q_out, void* k_cache, void* v_cache,
@@ -138,21 +142,21 @@ extern "C" int rlis_rope_cache(const void* qkv, void* q_out, void* k_cache, void
         const int items = (nh + 2 * nkv) * (d / 2 / vn);
         const int th = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
         if (dtype == RLIS_F32)
-            rope_cache_vec_kernel<float><<<n_tokens, th, smem, stream>>>(
+            rlis_launch(rope_cache_vec_kernel<float>, n_tokens, th, smem, stream, 
                 (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots, inv_freq,
                 nh, nkv, d, page_size);
         else
-            rope_cache_vec_kernel<bf16><<<n_tokens, th, smem, stream>>>(
+            rlis_launch(rope_cache_vec_kernel<bf16>, n_tokens, th, smem, stream, 
                 (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, inv_freq,
                 nh, nkv, d, page_size);
         return RLIS_LAUNCH_CHECK();
     }
     if (dtype == RLIS_F32)
-        rope_cache_kernel<float><<<n_tokens, threads, smem, stream>>>(
+        rlis_launch(rope_cache_kernel<float>, n_tokens, threads, smem, stream, 
             (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots,
             inv_freq, nh, nkv, d, page_size);
     else if (dtype == RLIS_BF16)
-        rope_cache_kernel<bf16><<<n_tokens, threads, smem, stream>>>(
+        rlis_launch(rope_cache_kernel<bf16>, n_tokens, threads, smem, stream, 
             (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots,
             inv_freq, nh, nkv, d, page_size);
     else

@@ -8,6 +8,7 @@
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               size_t total, int interleave) {
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     size_t t = idx / inter;
@@ -18,10 +19,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     float u = to_f<T>(gu[t * 2 * inter + ui]);
     float s = g / (1.0f + expf(-g));
     out[idx] = from_f<T>(s * u);
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // bfloat16, blocks of 4: 16 bytes in (4 gate, 4 up), 8 bytes out per step; two steps a thread.
 __global__ void swiglu_bf16_il4_kernel(const uint4* __restrict__ gu, uint2* __restrict__ out, size_t n_vec) {
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
     const uint4 v = gu[i];
@@ -37,6 +40,7 @@ __global__ void swiglu_bf16_il4_kernel(const uint4* __restrict__ gu, uint2* __re
     o.x = *reinterpret_cast<uint32_t*>(&o01);
     o.y = *reinterpret_cast<uint32_t*>(&o23);
     out[i] = o;
+    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_swiglu(const void* gu, void* out, int n_tokens, int inter, int interleave,
@@ -47,15 +51,15 @@ extern "C" int rlis_swiglu(const void* gu, void* out, int n_tokens, int inter, i
     const int threads = 256;
     if (dtype == RLIS_BF16 && interleave == 4) {
         const size_t n_vec = total / 4;      // inter % 4 == 0 was checked above
-        swiglu_bf16_il4_kernel<<<(unsigned)((n_vec + threads - 1) / threads), threads, 0, stream>>>(
+        rlis_launch(swiglu_bf16_il4_kernel, (unsigned)((n_vec + threads - 1) / threads), threads, 0, stream, 
             (const uint4*)gu, (uint2*)out, n_vec);
         return RLIS_LAUNCH_CHECK();
     }
     unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RLIS_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total, interleave);
+        rlis_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, inter, total, interleave);
     else if (dtype == RLIS_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total, interleave);
+        rlis_launch(swiglu_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gu, (bf16*)out, inter, total, interleave);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -257,7 +257,7 @@ class ModelRunner:
             return None
         W = 0 if st.logit_rows is None else st.logit_rows.shape[0]
         # the only way the contexts' lengths reach the launch configuration (ops.decode_splits)
-        return (st.n_seqs, W, min(st.max_decode_ctx // ops.DECODE_MIN_KEYS_PER_SPLIT, 64))
+        return (st.n_seqs, W, min(st.max_decode_ctx // ops.DECODE_MIN_KEYS_PER_SPLIT, 32))
 
     def forward(self, st: StepContext):
         """Launches the model on a prepared step; float32 logits [wanted, vocab] or None.  The

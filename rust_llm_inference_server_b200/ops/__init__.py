@@ -21,6 +21,13 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 launch_count = 0
 
 
+def set_programmatic_launch(on: bool) -> None:
+    """Launch kernels with the programmatic-serialization attribute (default off; also
+    RLIS_PDL=1): the next kernel's CTAs are launched while the current one drains; see
+    csrc/kernels/common.cuh."""
+    lib().rlis_set_pdl(1 if on else 0)
+
+
 def _code(dtype) -> int:
     try:
         return _DT[dtype]
@@ -117,6 +124,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 
 SKINNY_MAX_ROWS = 16
+SKINNY_MAX_FEATURES = 32768     # above this (the LM head) the library GEMM streams weights faster
 
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False) -> torch.Tensor:
@@ -146,7 +154,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
         raise KernelError(f"linear: expected matching float32 or bfloat16 operands, got {x.dtype}, {w.dtype}")
     if not x.is_cuda:
         raise KernelError("linear: expected CUDA tensors; there is no CPU path")
-    if x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+    if (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous()
+            and w.shape[0] < SKINNY_MAX_FEATURES):
         return skinny_gemm(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
@@ -220,11 +229,13 @@ DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
 def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
-    """How many pieces the context is cut into for decode attention: enough CTAs (kv heads x
-    requests x splits) to fill the SMs about four times, each piece at least 128 keys long (role
-    of `split_plan`, crates/model/src/paged_attention.rs:21-36, re-tuned for 148 SMs)."""
-    want = -(-4 * NUM_SMS // max(1, n_decode * n_kv_heads))
-    return max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 64))
+    """How many pieces the context is cut into for decode attention (role of `split_plan`,
+    crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs): enough CTAs
+    (kv heads x requests x splits) to fill the SMs about twice, four pieces for long contexts in
+    any case (it evens out the tail of large batches), each piece at least 128 keys long."""
+    want = -(-2 * NUM_SMS // max(1, n_decode * n_kv_heads))
+    want = max(want, min(4, max_ctx // 512))
+    return max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 32))
 
 
 def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, block_tables,
@@ -254,8 +265,7 @@ def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, blo
         ctx_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n, n_heads,
         n_kv_heads, head_dim, page_size, float(scale), int(window), int(splits), _code(q.dtype),
         _stream()), "attention_decode")
-    global launch_count
-    launch_count += 2 if splits > 1 else 1
+    _count()
     return out
 
 

@@ -7,6 +7,7 @@ first op raises.  Launchers return 0, a cudaError_t (> 0) or a negative library 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 from . import build
@@ -55,6 +56,10 @@ def lib():
                 raise KernelError(f"kernel library {path} lacks symbol {name}") from e
             fn.argtypes = args
             fn.restype = c_int
+        handle.rlis_set_pdl.argtypes = [c_int]
+        handle.rlis_set_pdl.restype = None
+        if os.environ.get("RLIS_PDL", "0") == "1":      # switch programmatic dependent launch on
+            handle.rlis_set_pdl(1)
         _lib = handle
     return _lib
 
