@@ -279,6 +279,8 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         cp_async_commit();
     };
 
+    // scores are kept in units of log2(e) (s * scale * log2 e): exp becomes a single exp2
+    const float scale_log2 = scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.f;      // of row g (every lane of a quad holds a copy)
     float oacc[ND][4];
 #pragma unroll
@@ -322,7 +324,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = (blk << 5) + nt * 8 + 2 * c + e;
-                const float sv = (key >= lo_all && key < ctx) ? sacc[nt][e] * scale : -INFINITY;
+                const float sv = (key >= lo_all && key < ctx) ? sacc[nt][e] * scale_log2 : -INFINITY;
                 p[nt][e] = sv;
                 mx = fmaxf(mx, sv);
             }
@@ -330,13 +332,13 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m_run, mx);          // finite: every block holds a visible key
-        const float corr = expf(m_run - m_new);
+        const float corr = exp2f(m_run - m_new);
         float lsum = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                p[nt][e] = expf(p[nt][e] - m_new);
+                p[nt][e] = exp2f(p[nt][e] - m_new);
                 lsum += p[nt][e];
             }
         lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
@@ -396,7 +398,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float mw = ml[(w * nrep + h) * 2];
             if (mw == -INFINITY) continue;              // this warp had no block of keys
-            const float wgt = expf(mw - big);
+            const float wgt = exp2f(mw - big);
             a += merge[((size_t)w * nrep + h) * D + j] * wgt;
             lsum += ml[(w * nrep + h) * 2 + 1] * wgt;
         }
@@ -407,7 +409,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             float* pr = partial + (((size_t)bi * nh + head) * splits + split) * (D + 2);
             pr[j] = a;
             if (j == 0) {
-                pr[D] = big;
+                pr[D] = big * 0.6931471805599453f;      // back to natural units, as the merge reads it
                 pr[D + 1] = lsum;
             }
         }

@@ -105,6 +105,7 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
         cp_async_commit();
     };
 
+    const float scale_log2 = scale * 1.4426950408889634f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float oacc[ND][4];
 #pragma unroll
@@ -138,15 +139,21 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
                 mma_bf16_16816(sacc[nt], qa[2 * ks2 + 1], kb[2], kb[3]);
             }
         }
-        // scale, hide keys after the query (and before its window), running softmax per row
+        // Scores in units of log2(e): s * scale * log2(e), so that exp(x) is one exp2 instruction
+        // (softmax does not see the common factor).  Keys after the query (and before its window)
+        // are hidden; tiles that lie wholly before every row's position skip the comparisons.
+        const bool edge = (kt + 1) * PF_BN - 1 > start_pos + t0 + warp * 16 || window > 0;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int key = kt * PF_BN + nt * 8 + 2 * c + e;
-                const float s0 = (key <= pos0 && key >= lo0) ? sacc[nt][e] * scale : -INFINITY;
-                const float s1 = (key <= pos1 && key >= lo1) ? sacc[nt][2 + e] * scale : -INFINITY;
+                float s0 = sacc[nt][e] * scale_log2, s1 = sacc[nt][2 + e] * scale_log2;
+                if (edge) {
+                    const int key = kt * PF_BN + nt * 8 + 2 * c + e;
+                    if (!(key <= pos0 && key >= lo0)) s0 = -INFINITY;
+                    if (!(key <= pos1 && key >= lo1)) s1 = -INFINITY;
+                }
                 sacc[nt][e] = s0;
                 sacc[nt][2 + e] = s1;
                 mx0 = fmaxf(mx0, s0);
@@ -159,13 +166,13 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         // a row that has seen no key yet (all hidden so far) keeps a zero state
         const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float corr0 = expf(m_run[0] - ms0), corr1 = expf(m_run[1] - ms1);   // exp(-inf) = 0
+        const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);   // exp2(-inf) = 0
         float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float p0 = expf(sacc[nt][e] - ms0), p1 = expf(sacc[nt][2 + e] - ms1);
+                const float p0 = exp2f(sacc[nt][e] - ms0), p1 = exp2f(sacc[nt][2 + e] - ms1);
                 sacc[nt][e] = p0;
                 sacc[nt][2 + e] = p1;
                 ls0 += p0;
