@@ -144,6 +144,34 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swig
     return out
 
 
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> torch.Tensor:
+    """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), bfloat16
+    operands.  epilogue "plain": bf16 [M, N]; "float32": float32 [M, N]; "swiglu4": w is a gate|up
+    matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, bf16 [M, N / 2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    _req(x, "x", torch.bfloat16)
+    _req(w, "w", torch.bfloat16, (N, K))
+    code = {"plain": 0, "swiglu4": 1, "float32": 2}[epilogue]
+    if M < 128 or N < 256 or K % 8 or N % (16 if code == 1 else 8):
+        raise KernelError(f"gemm_tcgen05: takes M >= 128, N >= 256, K a multiple of 8 and N a multiple of 8 "
+                          f"(16 with the SwiGLU epilogue); got M={M}, N={N}, K={K}")
+    out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.float32 if code == 2 else torch.bfloat16,
+                      device=x.device)
+    check(lib().rlis_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, code, _stream()),
+          "gemm_tcgen05")
+    _count()
+    return out
+
+
+def check_device_errors() -> None:
+    """Raises if a bounded wait inside a kernel ever ran out on this device (the kernel then
+    finished without its data; results since are not to be trusted).  Synchronises the device."""
+    code = lib().rlis_gemm_tcgen05_error()
+    if code != 0:
+        raise KernelError(f"gemm_tcgen05: a bounded mbarrier wait ran out on the device (code {code})")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
     """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
     16 rows go to this package's weight-streaming kernel, more to the library GEMM; both

@@ -136,7 +136,7 @@ def build_kernels() -> str:
     def cmd(out):
         if out == "OUT":
             return NVCC_FLAGS
-        return [_find_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs + ["-lcuda"]
+        return [_find_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs
 
     return _ensure("librlis_kernels.so", srcs, hdrs, cmd, "CUDA kernels (sm_100a)")
 

@@ -32,6 +32,7 @@ SIGNATURES = {
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
+    "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
 }
 
 OPTIONAL_SIGNATURES: dict = {}
@@ -56,6 +57,8 @@ def lib():
                 raise KernelError(f"kernel library {path} lacks symbol {name}") from e
             fn.argtypes = args
             fn.restype = c_int
+        handle.rlis_gemm_tcgen05_error.argtypes = []
+        handle.rlis_gemm_tcgen05_error.restype = c_int
         handle.rlis_set_pdl.argtypes = [c_int]
         handle.rlis_set_pdl.restype = None
         if os.environ.get("RLIS_PDL", "0") == "1":      # switch programmatic dependent launch on
