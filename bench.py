@@ -137,7 +137,7 @@ def run_reference(args) -> int:
     return 0
 
 
-def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: bool = True):
+def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: bool = True, clocks=None):
     """Device-timed decode: B requests, each step one teacher-forced token per request and the
     sampler kernel; the last step's context is `ctx_end`.  Returns (ms per step, launches per step)."""
     import numpy as np
@@ -167,6 +167,9 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: 
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     launches = 0
+    if clocks is not None:          # sample clocks over the warm-up and the timed steps only
+        clocks.start()
+        time.sleep(0.5)             # let nvidia-smi come up before anything is timed
     for i in range(total):
         if i == warmup:
             torch.cuda.synchronize()
@@ -186,7 +189,7 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: 
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both numbers are reported)")
@@ -263,11 +266,10 @@ def main() -> int:
     # ---- decode points at batch 1 and 64, then the headline batch under the clock sampler ----
     points = {}
     for b in (1, 64):
-        ms, _ = decode_run(llm, b, max(16, args.steps // 2), args.warmup, context, torch)
+        ms, _ = decode_run(llm, b, max(16, min(args.steps, 64)), args.warmup, context, torch)
         points[f"decode_b{b}"] = round(b / (ms / 1e3), 1)
     clocks = ClockSampler()
-    clocks.start()
-    ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch)
+    ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch, clocks=clocks)
     clk = clocks.stop()
     value = B / (ms / 1e3)
     mean_ctx = context - args.steps / 2

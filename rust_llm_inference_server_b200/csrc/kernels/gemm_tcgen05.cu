@@ -4,7 +4,7 @@
 // calls of its tensor library (crates/model/src/layers.rs:82,181-184); here it is a hand-written
 // sm_100a kernel so that SwiGLU never makes a round trip through HBM.
 //
-// One CTA computes a 128 x 256 tile.  Six warps, by role:
+// One persistent CTA per SM walks over 128 x 256 tiles.  Six warps, by role:
 //   warp 0, one lane: TMA producer.  Per k-block of 64 it asks for the 128 x 64 tile of x and the
 //           256 x 64 tile of W (cp.async.bulk.tensor, 128-byte swizzle) into a ring of 4 stages;
 //           an mbarrier per stage counts the bytes.
@@ -12,7 +12,8 @@
 //           descriptors into a 128 x 256 float32 accumulator in tensor memory; tcgen05.commit
 //           hands a stage back to the producer when the products that read it have finished, and
 //           tells the epilogue when the accumulator is complete.  The warp also owns the TMEM
-//           allocation (256 columns).
+//           allocation: all 512 columns, two accumulators, so that a tile's epilogue overlaps the
+//           next tile's products.
 //   warps 2-5: epilogue.  Each reads its quarter of the accumulator's lanes with tcgen05.ld, 32
 //           columns at a time, and stores bf16 (or float32) rows, or silu(gate) * up for a gate|up
 //           matrix whose rows are interleaved in blocks of 4.
@@ -115,16 +116,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 struct Ctrl {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t acc_full;
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     int abort;
 };
 
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // EPI 0: bf16 y [M, N].  EPI 1: SwiGLU, y [M, N / 2] bf16.  EPI 2: float32 y [M, N].
+// Persistent: CTA b works on tiles b, b + gridDim.x, ...; tile t -> (n tile t / m_tiles, m tile
+// t % m_tiles), so the CTAs that run together share a few column blocks of W and all of x in L2.
+// The accumulator is double-buffered in tensor memory (2 x 256 columns): the epilogue of a tile
+// overlaps the products of the next one.
 template <int EPI>
 __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
-                                                                  void* __restrict__ y, int M, int N, int K) {
+                                                                  void* __restrict__ y, int M, int N, int K,
+                                                                  int m_tiles, int num_tiles) {
     pdl_wait();
     extern __shared__ unsigned char gt_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gt_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -133,7 +144,6 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(b_tiles + (size_t)STAGES * B_STAGE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int k_blocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -142,104 +152,128 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
             bar_init(&ctrl->full[s], 1);
             bar_init(&ctrl->empty[s], 1);
         }
-        bar_init(&ctrl->acc_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            bar_init(&ctrl->acc_full[i], 1);
+            bar_init(&ctrl->acc_empty[i], 4);      // the four epilogue warps
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {   // tensor memory: 256 columns (128 lanes x 256 float32) for the accumulator
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(BN) : "memory");
+    if (warp == 1) {   // all of tensor memory: two accumulators of 128 lanes x 256 float32 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_acc = ctrl->tmem_base;
+    const uint32_t tmem_base = ctrl->tmem_base;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !bar_wait(&ctrl->empty[s], ((kb / STAGES) - 1) & 1, &ctrl->abort)) break;
-                bar_expect_tx(&ctrl->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
-                tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &map_x, kb * BK, m0, &ctrl->full[s]);
-                tma_load_2d(b_tiles + (size_t)s * B_STAGE_BYTES, &map_w, kb * BK, n0, &ctrl->full[s]);
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !ctrl->abort; tile += gridDim.x) {
+                const int n0 = (tile / m_tiles) * BN, m0 = (tile % m_tiles) * BM;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !bar_wait(&ctrl->empty[s], ((it / STAGES) - 1) & 1, &ctrl->abort)) break;
+                    bar_expect_tx(&ctrl->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+                    tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &map_x, kb * BK, m0, &ctrl->full[s]);
+                    tma_load_2d(b_tiles + (size_t)s * B_STAGE_BYTES, &map_w, kb * BK, n0, &ctrl->full[s]);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (!bar_wait(&ctrl->full[s], (kb / STAGES) & 1, &ctrl->abort)) break;
+            int it = 0, t = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !ctrl->abort; tile += gridDim.x, ++t) {
+                const int buf = t & 1;
+                if (t >= 2 && !bar_wait(&ctrl->acc_empty[buf], ((t >> 1) - 1) & 1, &ctrl->abort)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = smem_desc_sw128(a_tiles + (size_t)s * A_STAGE_BYTES);
-                const uint64_t bdesc = smem_desc_sw128(b_tiles + (size_t)s * B_STAGE_BYTES);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!bar_wait(&ctrl->full[s], (it / STAGES) & 1, &ctrl->abort)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t adesc = smem_desc_sw128(a_tiles + (size_t)s * A_STAGE_BYTES);
+                    const uint64_t bdesc = smem_desc_sw128(b_tiles + (size_t)s * B_STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K in the swizzled row
-                    umma_bf16(tmem_acc, adesc + (uint64_t)(k * UMMA_K * 2 >> 4), bdesc + (uint64_t)(k * UMMA_K * 2 >> 4),
-                              (kb | k) != 0 ? 1u : 0u);
-                umma_commit(&ctrl->empty[s]);              // the stage is free once these products are done
+                    for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K in the swizzled row
+                        umma_bf16(tmem_acc, adesc + (uint64_t)(k * UMMA_K * 2 >> 4), bdesc + (uint64_t)(k * UMMA_K * 2 >> 4),
+                                  (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&ctrl->empty[s]);              // the stage is free once these products are done
+                }
+                umma_commit(&ctrl->acc_full[buf]);
             }
-            umma_commit(&ctrl->acc_full);
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
         const int q = warp & 3;
-        const bool ok = bar_wait(&ctrl->acc_full, 0, &ctrl->abort);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int row = m0 + q * 32 + lane;
-        for (int cb = 0; cb < BN / 32; ++cb) {
-            uint32_t r[32];
-            tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), r);
-            const int col = n0 + cb * 32;
-            if (!ok || row >= M || col >= N) continue;
-            if (EPI == 0) {
-                bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * N + col;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+            const int buf = t & 1;
+            const int n0 = (tile / m_tiles) * BN, m0 = (tile % m_tiles) * BM;
+            const bool ok = bar_wait(&ctrl->acc_full[buf], (t >> 1) & 1, &ctrl->abort);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + q * 32 + lane;
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t r[32];
+                tmem_ld32(tmem_acc + (uint32_t)(cb * 32), r);
+                const int col = n0 + cb * 32;
+                if (!ok || row >= M || col >= N) continue;
+                if (EPI == 0) {
+                    bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * N + col;
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    if (col + v * 8 >= N) break;
-                    uint4 pk;
-                    pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                    pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                    pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                    pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                    *reinterpret_cast<uint4*>(o + v * 8) = pk;
-                }
-            } else if (EPI == 1) {
-                bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * (N >> 1) + (col >> 1);
-                float res[16];
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float gt = __uint_as_float(r[t * 8 + j]), up = __uint_as_float(r[t * 8 + 4 + j]);
-                        res[t * 4 + j] = gt / (1.0f + expf(-gt)) * up;
+                    for (int v = 0; v < 4; ++v) {
+                        if (col + v * 8 >= N) break;
+                        uint4 pk;
+                        pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                        pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                        pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                        pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                        *reinterpret_cast<uint4*>(o + v * 8) = pk;
                     }
+                } else if (EPI == 1) {
+                    bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * (N >> 1) + (col >> 1);
+                    float res[16];
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    if (col + v * 16 >= N) break;
-                    uint4 pk;
-                    pk.x = pack_bf16(res[v * 8 + 0], res[v * 8 + 1]);
-                    pk.y = pack_bf16(res[v * 8 + 2], res[v * 8 + 3]);
-                    pk.z = pack_bf16(res[v * 8 + 4], res[v * 8 + 5]);
-                    pk.w = pack_bf16(res[v * 8 + 6], res[v * 8 + 7]);
-                    *reinterpret_cast<uint4*>(o + v * 8) = pk;
-                }
-            } else {
-                float* o = reinterpret_cast<float*>(y) + (size_t)row * N + col;
+                    for (int tt = 0; tt < 4; ++tt)
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    if (col + v * 4 >= N) break;
-                    *reinterpret_cast<float4*>(o + v * 4) = make_float4(
-                        __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
-                        __uint_as_float(r[v * 4 + 3]));
+                        for (int j = 0; j < 4; ++j) {
+                            const float gt = __uint_as_float(r[tt * 8 + j]), up = __uint_as_float(r[tt * 8 + 4 + j]);
+                            res[tt * 4 + j] = gt / (1.0f + expf(-gt)) * up;
+                        }
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) {
+                        if (col + v * 16 >= N) break;
+                        uint4 pk;
+                        pk.x = pack_bf16(res[v * 8 + 0], res[v * 8 + 1]);
+                        pk.y = pack_bf16(res[v * 8 + 2], res[v * 8 + 3]);
+                        pk.z = pack_bf16(res[v * 8 + 4], res[v * 8 + 5]);
+                        pk.w = pack_bf16(res[v * 8 + 6], res[v * 8 + 7]);
+                        *reinterpret_cast<uint4*>(o + v * 8) = pk;
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(y) + (size_t)row * N + col;
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        if (col + v * 4 >= N) break;
+                        *reinterpret_cast<float4*>(o + v * 4) = make_float4(
+                            __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
+                            __uint_as_float(r[v * 4 + 3]));
+                    }
                 }
             }
+            // this warp has read its lanes of the buffer: hand it back to the product warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(&ctrl->acc_empty[buf]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
     pdl_trigger();   // the next kernel of the stream may start its launch
 }
@@ -290,7 +324,6 @@ extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, i
     if (epilogue == 1 && (N & 15) != 0) return RLIS_ERR_UNSUPPORTED;   // rows of N / 2 bf16 must stay 16-byte aligned
     if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
-    if ((M + BM - 1) / BM > 65535) return RLIS_ERR_UNSUPPORTED;
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, x, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return RLIS_ERR_UNSUPPORTED;
     static bool attr_done = false;
@@ -300,12 +333,15 @@ extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, i
         cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         attr_done = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    const int m_tiles = (M + BM - 1) / BM, num_tiles = m_tiles * ((N + BN - 1) / BN);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
     if (epilogue == 0)
-        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K);
+        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
     else if (epilogue == 1)
-        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K);
+        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
     else
-        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K);
+        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
     return RLIS_LAUNCH_CHECK();
 }

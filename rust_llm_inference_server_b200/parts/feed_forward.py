@@ -38,9 +38,13 @@ class SwiGLU(FeedForward):
         self.w_down = src.get(s.down_proj).contiguous()
 
     def forward(self, x, step):
-        if (self.dtype == torch.bfloat16 and self.interleave == 4 and x.shape[0] <= ops.SKINNY_MAX_ROWS
-                and self.spec.hidden % 8 == 0):
+        fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
+        if fusable and x.shape[0] <= ops.SKINNY_MAX_ROWS:
             act = ops.skinny_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
+        elif fusable and x.shape[0] >= 128 and self.spec.intermediate % 128 == 0:
+            # prefill: the tcgen05 product with the gating in its epilogue (the gate|up activations
+            # never reach HBM)
+            act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu4")
         else:
             gu = ops.linear(x, self.w_gate_up)
             act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)

@@ -126,6 +126,29 @@ def test_skinny_product_with_gating_and_interleaved_gating_kernel(I, K, M):
         assert bool(((out.double().cpu() - w2).abs() <= 2.0 ** -7 * w2.abs() + 1e-5).all())
 
 
+@pytest.mark.parametrize("shape,epilogue", [((128, 256, 64), "float32"), ((128, 256, 512), "float32"), ((300, 520, 200), "plain"),
+                                            ((129, 264, 8), "float32"), ((333, 1008, 96), "swiglu4"),
+                                            ((2048, 2048, 2048), "plain"), ((1024, 4096, 2048), "swiglu4"),
+                                            ((700, 1536, 8192), "plain")])
+def test_tcgen05_product_with_its_epilogues(shape, epilogue):
+    """The TMA-fed tensor-memory GEMM against a float32 product: whole tiles, ragged M, N and K,
+    many tiles a CTA (both accumulator buffers in use), and the SwiGLU epilogue."""
+    from rust_llm_inference_server_b200 import ops
+    M, N, K = shape
+    torch.manual_seed(M + N)
+    x, w = torch.randn(M, K).bfloat16(), (torch.randn(N, K) * 0.05).bfloat16()
+    got = ops.gemm_tcgen05(dev(x), dev(w), epilogue).float().cpu()
+    ops.check_device_errors()                      # no bounded wait ran out
+    want = (x.double() @ w.double().t())
+    if epilogue == "swiglu4":
+        r = want.view(M, -1, 2, 4)
+        want = (torch.nn.functional.silu(r[:, :, 0]) * r[:, :, 1]).reshape(M, N // 2)
+    rel = 2.0 ** -20 if epilogue == "float32" else 2.0 ** -7
+    assert bool(((got.double() - want).abs() <= rel * want.abs() + 1e-5 * max(1.0, math.sqrt(K))).all())
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05(dev(x[:64].contiguous()), dev(w), epilogue)        # fewer than 128 rows: refused
+
+
 def cache_from(k, v, page_size, n_pages, seed=0):
     """Scatters contiguous k, v [(requests) x (len, nkv, d)] into a paged cache with shuffled,
     interleaved pages; returns caches [pages, nkv, page, d] and the block tables."""
