@@ -19,7 +19,7 @@
 //           matrix whose rows are interleaved in blocks of 4.
 // Rows and columns past M, N and K are zero-filled by TMA and never stored.
 //
-// Every mbarrier wait is bounded by a second of wall time.  A wait that runs out sets an error word
+// Every mbarrier wait is bounded by a fifth of a second of wall time.  A wait that runs out sets an error word
 // (rlis_gemm_tcgen05_error), lets every role run to its end without further waiting, and the
 // CTA still frees its tensor memory before it returns.
 #include "common.cuh"
@@ -32,7 +32,7 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2;
 constexpr int GT_THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 1000000000ull;
+constexpr unsigned long long WAIT_LIMIT_NS = 200000000ull;   // a fifth of a second
 constexpr size_t GT_SMEM = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /* alignment */ + 256;
 
 __device__ int g_gemm_error = 0;

@@ -14,9 +14,12 @@
 // decode step is in flight at once; x is small and comes from L1.  The warps' partial sums meet
 // in shared memory and are added in warp order (deterministic).
 //
-// (Two other arrangements were measured on the LM-head shape, 128256 x 2048, 8 rows, and lost:
-// a persistent CTA per SM fed by cp.async.bulk copies through an mbarrier ring, 158 us, and a
-// persistent CTA with register double-buffering, 131 us.  The library GEMM takes 85 us there, so
+// (Other arrangements were measured on the LM-head shape, 128256 x 2048, 8 rows, and lost:
+// a persistent CTA per SM fed by cp.async.bulk copies through an mbarrier ring with the warps
+// splitting K, 158 us; the same ring with each warp owning whole tiles (no sums across warps),
+// 160 us: six warps an SM cannot hide the latency of the dependent tensor instructions and of
+// the x loads; a persistent CTA with register double-buffering, 131 us.  This one, with two to
+// seven CTAs of eight warps an SM, takes 97 us.  The library GEMM takes 85 us there, so
 // products with very many output features are left to it, see ops.linear.)
 //
 // Epilogues: plain (bf16 or float32 out), or SwiGLU on a gate|up matrix whose rows are interleaved
