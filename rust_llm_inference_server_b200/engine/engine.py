@@ -17,7 +17,7 @@ from .. import ops
 from ..cache import CacheStorage, host, plan_groups, size_groups
 from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import Sampler, float_bits
 from .runner import ModelRunner, StepEntry
 
 
@@ -120,6 +120,10 @@ class LLMEngine:
         self._params_dev = torch.empty((cfg.max_num_seqs, 2), dtype=torch.int32, device=model.device)
         self._ids_dev = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
         self._ids_host = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
+        self._fparams_host = torch.empty((cfg.max_num_seqs, 5), dtype=torch.int32, pin_memory=True)
+        self._fparams_dev = torch.empty((cfg.max_num_seqs, 5), dtype=torch.int32, device=model.device)
+        self._fids_dev = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
+        self._fids_host = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
 
     # ---- intake ----
 
@@ -195,31 +199,51 @@ class LLMEngine:
         return finished
 
     def _sample(self, logits: torch.Tensor, rows: list) -> list:
+        """One token per caught-up request.  Greedy and temperature rows: the device's Gumbel-max
+        kernel; top-k / top-p rows: the device's filtering kernel; rows with a repetition penalty:
+        the host (crates/engine/src/engine.rs:643-708 has the same split, with all filtering on
+        the host).  Only token ids come back, except for host rows."""
         n = len(rows)
-        modes = [s.sampler.device_mode(len(s.tokens)) for s in rows]
+        pos = [len(s.tokens) for s in rows]
+        plain = [s.sampler.device_mode(p) for s, p in zip(rows, pos)]
+        filt = [s.sampler.filtered_mode(p) if m is None else None for s, p, m in zip(rows, pos, plain)]
         out = [0] * n
-        dev_idx = [i for i, m in enumerate(modes) if m is not None]
-        if dev_idx:
+        launched = False
+        if any(m is not None for m in plain):
             ph = self._params_host.numpy().view(np.uint32)
             for i in range(n):
-                ph[i] = modes[i] if modes[i] is not None else (0, 0)
+                ph[i] = plain[i] if plain[i] is not None else (0, 0)
             self._params_dev[:n].copy_(self._params_host[:n], non_blocking=True)
-            ids = ops.sample_rows(logits, self._params_dev[:n], self._ids_dev[:n])
-            self._ids_host[:n].copy_(ids, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            got = self._ids_host[:n].tolist()
+            ops.sample_rows(logits, self._params_dev[:n], self._ids_dev[:n])
+            self._ids_host[:n].copy_(self._ids_dev[:n], non_blocking=True)
             self.stats.h2d_bytes += n * 8
+            launched = True
+        if any(f is not None for f in filt):
+            fh = self._fparams_host.numpy().view(np.uint32)
+            for i in range(n):
+                fh[i] = filt[i] if filt[i] is not None else (float_bits(1.0), 1, float_bits(1.0), 0, 0)
+            self._fparams_dev[:n].copy_(self._fparams_host[:n], non_blocking=True)
+            ops.sample_filtered(logits, self._fparams_dev[:n], self._fids_dev[:n])
+            self._fids_host[:n].copy_(self._fids_dev[:n], non_blocking=True)
+            self.stats.h2d_bytes += n * 20
+            launched = True
+        if launched:
+            torch.cuda.current_stream().synchronize()
             self.stats.d2h_bytes += n * 4
-            for i in dev_idx:
-                out[i] = got[i]
-        host_idx = [i for i, m in enumerate(modes) if m is None]
+            a, b = self._ids_host[:n].tolist(), self._fids_host[:n].tolist()
+            for i in range(n):
+                if plain[i] is not None:
+                    out[i] = a[i]
+                elif filt[i] is not None:
+                    out[i] = b[i]
+        host_idx = [i for i in range(n) if plain[i] is None and filt[i] is None]
         if host_idx:
             sel = torch.tensor(host_idx, device=logits.device)
             rows_host = logits.index_select(0, sel).to("cpu").numpy()
             self.stats.d2h_bytes += rows_host.nbytes
             for j, i in enumerate(host_idx):
                 s = rows[i]
-                out[i] = s.sampler.sample_host(rows_host[j], s.tokens, len(s.tokens))
+                out[i] = s.sampler.sample_host(rows_host[j], s.tokens, pos[i])
         return out
 
     def _accept(self, s: _Sequence, token: int, now: float):

@@ -374,6 +374,23 @@ def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | 
     return out
 
 
+def sample_filtered(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token id per row of float32 logits [R, V] by temperature sampling with top-k and/or
+    top-p filtering on the device.  params int32 [R, 5] = (bits of 1/T, top_k (0: off), bits of
+    top_p, low word, high word of a 53-bit uniform).  Returns int32 [R]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise KernelError("sample_filtered: logits must be float32 CUDA rows with unit stride")
+    _req(params, "params", torch.int32, (R, 5))
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _req(out, "out", torch.int32, (R,))
+    check(lib().rlis_sample_filtered(logits.data_ptr(), params.data_ptr(), out.data_ptr(), R, V,
+                                     logits.stride(0), _stream()), "sample_filtered")
+    _count()
+    return out
+
+
 def nll_rows(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     """Negative log-likelihood of targets[r] under softmax(logits[r]); float32 [R]."""
     R, V = logits.shape

@@ -280,3 +280,55 @@ def filtered_distribution(logits, temperature: float, top_k: int, top_p: float) 
     for i in order:
         p[i] = w[i]
     return p / p.sum()
+
+
+def uniform_53(seed: int, position: int) -> int:
+    """The engine's uniform for top-k / top-p rows as a 53-bit integer (u = this / 2^53): two
+    rounds of the splitmix64 finaliser over (seed, position).  (The reference seeds a ChaCha8
+    stream per request, crates/engine/src/sampler.rs:57-66; a hash of the position instead makes a
+    draw independent of how many draws came before, so a preempted request repeats its tokens.)"""
+    m = (1 << 64) - 1
+
+    def mix(x):
+        x = (x + 0x9E3779B97F4A7C15) & m
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & m
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & m
+        return x ^ (x >> 31)
+
+    return mix(mix(seed & m) ^ (position & m)) >> 11
+
+
+def filtered_sample(logits, temperature: float, top_k: int, top_p: float, u53: int) -> int:
+    """The engine's rule for top-k / top-p rows, restated slowly with Python integers.  Filtering
+    as crates/engine/src/sampler.rs:116-209: the k highest logits (ties: lower id first), the
+    shortest descending prefix whose share of the mass reaches top_p, the crossing token included.
+    The reference then draws from the descending order with a ChaCha8 stream; here weights are
+    fixed-point, w = floor(float32 exp((l - max) / T) * 2^40), and the draw is by inverse CDF in
+    vocabulary order with the uniform u53 / 2^53: r = floor(u * kept mass), the first kept token
+    whose running mass exceeds r."""
+    l = np.asarray(logits, dtype=np.float32)
+    inv_t = np.float32(1.0) / np.float32(temperature)
+    w = [int(np.float32(np.exp(np.float32((x - l.max()) * inv_t), dtype=np.float32) * np.float32(2.0 ** 40))) for x in l]
+    order = sorted(range(len(l)), key=lambda i: (-float(l[i]), i))
+    if 0 < top_k < len(l):
+        order = order[:top_k]
+    mass = sum(w[i] for i in order)
+    if np.float32(top_p) < 1:
+        target = int(float(np.float32(top_p)) * float(mass))
+        acc, keep = 0, len(order)
+        for j, i in enumerate(order):
+            acc += w[i]
+            if acc >= target:
+                keep = j + 1
+                break
+        order = order[:keep]
+    kept = set(order)
+    total = sum(w[i] for i in kept)
+    r = ((u53 << 11) * total) >> 64
+    acc = 0
+    for v in range(len(l)):
+        if v in kept:
+            acc += w[v]
+            if acc > r:
+                return v
+    return 0

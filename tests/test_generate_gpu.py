@@ -129,6 +129,14 @@ def test_seeded_sampling_is_reproducible_and_ignores_neighbours(model_root):
         lg = P.forward_logits(w, CONFIGS[which], toks)[-1].numpy()
         assert P.sample_row(lg, 0.8, P.row_key(3, len(toks))) == t
         toks.append(t)
+    # top-k / top-p rows are filtered and drawn on the device: replay with the plain rule
+    sp = SamplingParams(max_tokens=6, temperature=0.9, top_k=12, top_p=0.85, seed=11)
+    got = llm.generate([prompts[1]], sp)[0].token_ids
+    toks = list(prompts[1])
+    for t in got:
+        lg = P.forward_logits(w, CONFIGS[which], toks)[-1].numpy()
+        assert P.filtered_sample(lg, 0.9, 12, 0.85, P.uniform_53(11, len(toks))) == t
+        toks.append(t)
 
 
 def test_end_of_sequence_and_limits(model_root, tmp_path):

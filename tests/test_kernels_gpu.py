@@ -423,3 +423,38 @@ def test_kernels_refuse_what_they_do_not_take():
                               z.clone(), i, i, torch.zeros(1, 1, dtype=torch.int32, device="cuda"), 1, 1, 40, 4, 1.0)
     with pytest.raises(KernelError, match="not supported"):
         ops.swiglu(dev(torch.randn(2, 8).half()), dev(torch.randn(2, 4).half()))
+
+
+def test_filtered_sampling_on_the_device_equals_the_plain_rule():
+    """Top-k / top-p rows: the kernel picks the token the plain rule picks, row by row, whatever
+    its neighbours; frequencies follow the filtered softmax."""
+    from rust_llm_inference_server_b200 import ops
+    rng = np.random.default_rng(5)
+    R, V = 24, 1003
+    logits = (rng.normal(size=(R, V)) * 2.5).astype(np.float32)
+    logits[3, [7, 500, 900]] = logits[3].max()                # exact ties at the top
+    logits[[4, 8, 9]] = 0.25                                  # all equal: the lowest ids are the kept ones
+    logits[13, 100:160] = np.sort(logits[13])[-30]            # sixty ties across the 40th place
+    logits[14, 300:420] = np.sort(logits[14])[-4]             # ties across the top-10 and the nucleus edge
+    settings = [(0.8, 0, 0.9), (1.0, 40, 1.0), (0.5, 10, 0.5), (1.4, 0, 0.3), (0.9, 1, 1.0), (1.0, 2000, 0.95)]
+    params = np.zeros((R, 5), dtype=np.uint32)
+    want = []
+    for r in range(R):
+        T, k, p = settings[r % len(settings)]
+        u = (rng.integers(0, 1 << 53, dtype=np.uint64))
+        params[r] = (np.float32(np.float32(1.0) / np.float32(T)).view(np.uint32), k, np.float32(p).view(np.uint32),
+                     int(u) & 0xFFFFFFFF, int(u) >> 32)
+        want.append(P.filtered_sample(logits[r], T, k, p, int(u)))
+    lt = torch.from_numpy(logits).cuda()
+    got = ops.sample_filtered(lt, torch.from_numpy(params.view(np.int32)).cuda()).cpu().tolist()
+    assert got == want
+    alone = ops.sample_filtered(lt[5:6], torch.from_numpy(params.view(np.int32)[5:6].copy()).cuda()).cpu().tolist()
+    assert alone == [want[5]]
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 1.5]]).cuda().repeat(6000, 1)
+    ps_ = np.zeros((6000, 5), dtype=np.uint32)
+    us = rng.integers(0, 1 << 53, size=6000, dtype=np.uint64)
+    for i in range(6000):
+        ps_[i] = (np.float32(1 / 0.7).view(np.uint32), 4, np.float32(0.8).view(np.uint32), int(us[i]) & 0xFFFFFFFF, int(us[i]) >> 32)
+    ids = ops.sample_filtered(small, torch.from_numpy(ps_.view(np.int32)).cuda()).cpu().numpy()
+    freq = np.bincount(ids, minlength=6) / 6000
+    assert np.abs(freq - P.filtered_distribution(np.array([0.0, 1.0, 2.0, -1.0, 0.5, 1.5], np.float32), 0.7, 4, 0.8)).max() < 0.03

@@ -64,3 +64,29 @@ def test_same_seed_same_tokens_other_seed_other_tokens():
     b = [Sampler(SamplingParams(temperature=1.0, top_p=0.95, seed=11)).sample_host(logits, [], i) for i in range(40)]
     c = [Sampler(SamplingParams(temperature=1.0, top_p=0.95, seed=12)).sample_host(logits, [], i) for i in range(40)]
     assert a == b and a != c
+
+
+def test_filtered_draw_equals_the_plain_rule_and_follows_the_filtered_softmax():
+    from rust_llm_inference_server_b200.sampling import filtered_draw, unit_uniform_53
+    rng = np.random.default_rng(1)
+    for trial in range(30):
+        n = int(rng.integers(5, 300))
+        logits = (rng.normal(size=n) * rng.uniform(0.5, 4)).astype(np.float32)
+        if trial % 5 == 0:
+            logits[rng.integers(0, n, size=3)] = logits.max()          # exact ties at the top
+        T, k, p = float(rng.uniform(0.3, 1.5)), int(rng.integers(0, n + 3)), float(rng.choice([1.0, 0.9, 0.5, 0.1]))
+        if k == 0 and p >= 1.0:
+            p = 0.9
+        for pos in range(4):
+            u = unit_uniform_53(trial, pos)
+            assert u == P.uniform_53(trial, pos)
+            want = P.filtered_sample(logits, T, k, p, u)
+            got = filtered_draw(logits, np.float32(1.0) / np.float32(T), k, p, u)
+            assert got == want, (trial, pos, n, T, k, p)
+    logits = (rng.normal(size=40) * 2).astype(np.float32)
+    for T, k, p in ((0.8, 0, 0.9), (1.3, 5, 1.0), (1.0, 12, 0.6)):
+        counts = np.zeros(40)
+        for i in range(20000):
+            counts[filtered_draw(logits, np.float32(1.0) / np.float32(T), k, p, unit_uniform_53(99, i))] += 1
+        want = P.filtered_distribution(logits, T, k, p)
+        assert np.abs(counts / 20000 - want).max() < 0.015
