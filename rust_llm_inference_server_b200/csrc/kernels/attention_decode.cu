@@ -32,7 +32,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int d, int page_size,
     float scale, int window, int splits) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     extern __shared__ __align__(16) float smem[];
     // smem: q [NREP][d] | p per warp [DEC_WARPS][32][NREP] | merge area
     float* qs = smem;
@@ -191,7 +191,6 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
             }
         }
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // Tensor-core version for head sizes 64 and 128 (groups of up to 8 query heads).  The CUDA-core
@@ -211,7 +210,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
     float scale, int window, int splits, int* __restrict__ tickets) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     __shared__ int s_last;
     constexpr int STRIDE = D + 8;            // elements per padded row
     constexpr int KS = D / 16;               // k-steps of Q K^T
@@ -442,7 +441,6 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             if (threadIdx.x == 0) tickets[bi * nkv + kvh] = 0;
         }
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // Ticket counters of the fused merge, part of the library image, zero between launches.
@@ -458,7 +456,7 @@ template <int D> constexpr size_t decode_mma_smem_bytes() {
 __global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                            const int* __restrict__ dec_rows, int nh, int d,
                                            int splits) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     const int bi = blockIdx.y, head = blockIdx.x;
     const float* pr = partial + ((size_t)bi * nh + head) * splits * (d + 2);
     float big = -INFINITY;
@@ -474,7 +472,6 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ partial, bf
         }
         out[((size_t)row * nh + head) * d + j] = from_f<bf16>(a / lsum);
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 size_t decode_smem_bytes(int nrep, int d) {

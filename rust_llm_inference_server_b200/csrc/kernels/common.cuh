@@ -76,17 +76,26 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // ---- programmatic dependent launch --------------------------------------------------------
 // Every kernel of this library calls pdl_wait() before it touches anything an earlier kernel of
-// the stream may write (or may still read), and pdl_trigger() as its CTAs finish.  Launched with
-// the programmatic-serialization attribute, the next kernel's CTAs are then launched while this
-// kernel's last CTAs drain, and run their prologue (the first weight vectors of a weight-streaming
-// product) before they wait; without the attribute both calls do nothing.  Before pdl_wait() a
-// kernel may read only memory that no kernel of the step writes: weights and index arrays.
-// (Triggering at the top of a kernel instead lets kernels pile up several deep, each holding SM
-// slots while it waits; the decode step ran a fifth slower that way.)
+// the stream may write (or may still read), and pdl_trigger() when the next kernel may be launched
+// beside it.  Launched with the programmatic-serialization attribute, the next kernel's CTAs then
+// run their prologue (the first weight tiles of a weight-streaming product) before they wait for
+// this kernel to finish; without the attribute both calls do nothing.  Before pdl_wait() a kernel
+// may read only memory that no kernel of the step writes (weights, tensor maps) and write nothing.
+// A kernel triggers only after its own wait: triggering at the top lets kernels pile up several
+// deep, each holding SM slots while it waits, and the decode step ran a fifth slower that way.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// For the short kernels of the decode step, and for those whose successor has weights to request:
+// once this kernel's own dependency is resolved the next kernel may be launched beside it.  It runs
+// its prologue (for the weight-streaming product: requests its first stages of weights) and then
+// waits for this kernel to finish.  Only after the wait, so that never more than one kernel is
+// queued up behind the running one.
+__device__ __forceinline__ void pdl_wait_and_trigger() {
+    pdl_wait();
+    pdl_trigger();
+}
 
-extern int g_rlis_pdl;   // 0 (default): plain launches; see rlis_set_pdl in pdl.cu
+extern int g_rlis_pdl;   // 1 (default): launches carry the attribute; see rlis_set_pdl in pdl.cu
 
 template <typename... KArgs, typename... Args>
 static inline void rlis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -101,5 +110,26 @@ static inline void rlis_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_rlis_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same for a grid of thread-block clusters of `cluster` CTAs.
+template <typename... KArgs, typename... Args>
+static inline void rlis_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, dim3 cluster, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rlis_pdl ? 2 : 1;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }

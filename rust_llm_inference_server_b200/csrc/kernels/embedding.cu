@@ -6,7 +6,7 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -16,7 +16,6 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     }
     const T* row = table + (size_t)id * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f<T>(row[i]);
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_embedding(const int* ids, const void* table, float* out, int n_tokens,

@@ -1,4 +1,4 @@
-// Warp-level tensor-core helpers shared by the attention and skinny-GEMM kernels: asynchronous
+// Warp-level tensor-core helpers shared by the attention kernels: asynchronous
 // 16-byte copies into shared memory, ldmatrix, and the bf16 m16n8k16 product with float32
 // accumulators.
 //

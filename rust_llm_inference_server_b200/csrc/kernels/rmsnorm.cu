@@ -15,7 +15,7 @@ template <typename T>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ rows, int hidden, float eps) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     __shared__ float scratch[33];
     const size_t obase = (size_t)blockIdx.x * hidden;
     if (rows != nullptr) {
@@ -51,7 +51,6 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ 
     const float rstd = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         out[base + i] = from_f<T>(resid[base + i] * rstd * w[i]);
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // The same for widths that are multiples of 4: 16-byte accesses, and the row is kept
@@ -81,7 +80,7 @@ template <typename T>
 __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                     const float* __restrict__ w, T* __restrict__ out,
                                     const int* __restrict__ rows, int hidden, float eps) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     __shared__ float scratch[33];
     constexpr int MAXV = 4;
     const size_t obase = (size_t)blockIdx.x * hidden;
@@ -118,7 +117,6 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restri
                              make_float4(x.x * rstd * ww.x, x.y * rstd * ww.y, x.z * rstd * ww.z, x.w * rstd * ww.w));
         }
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_rmsnorm(float* resid, const void* delta, const float* w, void* out,

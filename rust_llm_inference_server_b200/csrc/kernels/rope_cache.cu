@@ -15,7 +15,7 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ positions, const int* __restrict__ slots,
                                   const float* __restrict__ inv_freq, int nh, int nkv, int d,
                                   int page_size) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     extern __shared__ float cs[];  // cos[half], sin[half]
     const int t = blockIdx.x;
     const int half = d >> 1;
@@ -62,7 +62,6 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
             }
         }
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 // The same with 16-byte accesses: a thread takes one vector of the first half of a head and the
@@ -73,7 +72,7 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
                                       const int* __restrict__ positions, const int* __restrict__ slots,
                                       const float* __restrict__ inv_freq, int nh, int nkv, int d,
                                       int page_size) {
-    pdl_wait();
+    pdl_wait_and_trigger();
     constexpr int VN = Vec16<T>::N;
     extern __shared__ float cs[];
     const int t = blockIdx.x;
@@ -126,7 +125,6 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
         *reinterpret_cast<uint4*>(dst + j0) = o1;
         *reinterpret_cast<uint4*>(dst + half + j0) = o2;
     }
-    pdl_trigger();   // the next kernel of the stream may start its launch
 }
 
 extern "C" int rlis_rope_cache(const void* qkv, void* q_out, void* k_cache, void* v_cache,

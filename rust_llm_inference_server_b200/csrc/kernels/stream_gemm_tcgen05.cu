@@ -1,0 +1,282 @@
+// Weight-streaming matrix product for the decode step on the fifth-generation tensor cores:
+//   y[M, N] = x[M, K] W[N, K]^T,  bf16 operands, float32 accumulation, M (tokens) up to 128.
+// Role of the reference's small-batch GEMV (crates/model/src/gemv.metal:24-94: every weight block
+// read once for all rows of the batch).  With a handful of rows the product is a pure stream of W
+// from HBM, so the kernel is built to keep bytes in flight with almost no instructions:
+//
+//   * the weights are the M side of the tensor instruction: a CTA owns 128 output features and a
+//     range of k; a 128 x 64 tile of W (16 KB) arrives by ONE bulk tensor copy (TMA, 128-byte
+//     swizzle) into a ring of 4 stages, together with the NT x 64 tile of x (NT = tokens rounded
+//     up to 16, 32, 64 or 128; rows past M are zero-filled by TMA);
+//   * one thread issues tcgen05.mma (M 128, N NT, K 16) into a 128 x NT float32 accumulator in
+//     tensor memory; tcgen05.commit frees the stage;
+//   * four warps read the accumulator (a lane = a feature, a column = a token) and store.
+// Matrices with few features would fill few SMs, so k is split over the CTAs of a thread-block
+// cluster (grid = feature tiles x splits, 2 to 16 splits, more CTAs than SMs and all resident at
+// once: the whole matrix is requested in the first microsecond).  Each CTA of the cluster leaves
+// its float32 partial sums in its own shared memory; after a cluster barrier CTA r adds, for the
+// tokens r, r + splits, ..., the partial sums of all CTAs through distributed shared memory in
+// the order of the splits, so the result does not depend on timing and nothing passes through
+// global memory.  The number of splits depends on N and K only, never on the rows, so a token's
+// result does not depend on its neighbours.
+//
+// The first stages of W are requested before the kernel waits for its predecessor in the stream
+// (programmatic dependent launch): weights are written by nobody, so the stream of weights goes
+// on across the kernel boundary, and only x and y wait.
+//
+// (Measured on the four products of a 1B Llama layer, 8 rows, 121.6 MB of weights, replayed back
+// to back from a graph: an mma.sync kernel fed by 16-byte cp.async copies into per-lane slots,
+// 8 features a CTA with its warps splitting k, took 42.0 us a layer, bound by instruction issue
+// (about 60 instructions per 512 bytes) and by re-reading x in every CTA; variants of it with bulk
+// copies and an mbarrier ring, with whole tiles per warp, or persistent with register double
+// buffering were slower still.  This kernel takes 38.4 us without and 34.4 us with the early
+// weight requests; the LM head, 525 MB, takes 80 us, the time of a plain copy.  Summing the
+// splits through global memory with a ticket per tile instead of the cluster cost 5 us a product.)
+//
+// Epilogues: bf16 or float32 y, or SwiGLU on a gate|up matrix whose rows are interleaved in blocks
+// of 4 (rows 8t..8t+3 gate, 8t+4..8t+7 up): y[m, 4t + j] = silu(gate_j) * up_j.
+//
+// Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets an error word
+// (rlis_stream_gemm_error), every role runs to its end without further waits, and the CTA frees
+// its tensor memory before it returns.
+#include "tcgen05_utils.cuh"
+#include <math.h>
+
+namespace {
+using namespace tc;
+constexpr int SF = 128;                 // features of a CTA (the M side of the instruction)
+constexpr int SK = 64;                  // k of a stage: 128 bytes of bf16, one swizzle row
+constexpr int S_STAGES = 4;
+constexpr int W_STAGE_BYTES = SF * SK * 2;
+constexpr int S_THREADS = 128;
+constexpr int MAX_SPLITS = 16;          // the largest cluster (above 8 is opt-in)
+
+template <int NT> constexpr size_t stream_smem_bytes() {
+    return (size_t)S_STAGES * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 128;
+}
+
+struct SCtrl {
+    uint64_t full[S_STAGES];
+    uint64_t empty[S_STAGES];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Reads a float at the same shared-memory offset in the cluster's CTA `rank`.
+__device__ __forceinline__ float ld_dsmem(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int EPI, typename OutT>
+__device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t, int f, int lane, int N) {
+    if (EPI == 1) {
+        // lanes 8i..8i+3 hold gate, 8i+4..8i+7 the matching up values
+        const float other = __shfl_xor_sync(0xffffffffu, v, 4);
+        if ((lane & 4) == 0 && f + 4 < N)
+            y[(size_t)t * (N >> 1) + ((f >> 3) << 2) + (f & 3)] = from_f<OutT>(v / (1.0f + expf(-v)) * other);
+    } else if (f < N) {
+        y[(size_t)t * N + f] = from_f<OutT>(v);
+    }
+}
+
+template <int NT, int EPI, typename OutT>
+__global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x,
+                                                                OutT* __restrict__ y, int M, int N, int K,
+                                                                int kb_per_split) {
+    extern __shared__ unsigned char sg_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sg_smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int X_STAGE_BYTES = NT * SK * 2;
+    constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+    constexpr uint32_t IDESC = idesc_bf16(SF, NT);
+    unsigned char* w_tiles = base;
+    unsigned char* x_tiles = base + (size_t)S_STAGES * W_STAGE_BYTES;
+    SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)S_STAGES * X_STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
+    const int n0 = tile * SF;
+    const int k_blocks = (K + SK - 1) / SK;
+    const int kb0 = split * kb_per_split;
+    const int kb1 = min(kb0 + kb_per_split, k_blocks);
+    const bool has_work = kb0 < kb1;                        // a split past the end of k adds zeros
+
+    if (threadIdx.x == 0) {
+        ctrl->abort = 0;
+        for (int s = 0; s < S_STAGES; ++s) {
+            bar_init(&ctrl->full[s], 1);
+            bar_init(&ctrl->empty[s], 1);
+        }
+        bar_init(&ctrl->acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // producer: one bulk tensor copy per 16 KB of W.  No kernel writes the weights, so the first
+        // stages of W are requested before this grid's dependency on the previous kernel of the
+        // stream is resolved (programmatic dependent launch); x and y wait for it.
+        const int n_kb = kb1 - kb0;
+        const int early = n_kb < S_STAGES ? n_kb : S_STAGES;
+        for (int it = 0; it < early; ++it) {
+            bar_expect_tx(&ctrl->full[it], W_STAGE_BYTES + X_STAGE_BYTES);
+            tma_load_2d(w_tiles + (size_t)it * W_STAGE_BYTES, &map_w, (kb0 + it) * SK, n0, &ctrl->full[it]);
+        }
+        pdl_wait();
+        for (int it = 0; it < early; ++it)
+            tma_load_2d(x_tiles + (size_t)it * X_STAGE_BYTES, &map_x, (kb0 + it) * SK, 0, &ctrl->full[it]);
+        for (int it = early; it < n_kb; ++it) {
+            const int s = it % S_STAGES, kb = kb0 + it;
+            if (!bar_wait(&ctrl->empty[s], ((it / S_STAGES) - 1) & 1, &ctrl->abort)) break;
+            bar_expect_tx(&ctrl->full[s], W_STAGE_BYTES + X_STAGE_BYTES);
+            tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &map_w, kb * SK, n0, &ctrl->full[s]);
+            tma_load_2d(x_tiles + (size_t)s * X_STAGE_BYTES, &map_x, kb * SK, 0, &ctrl->full[s]);
+        }
+        pdl_trigger();     // everything this CTA reads is requested: the next kernel may start its own requests
+    } else if (warp == 1 && lane == 0) {
+        for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+            const int s = it % S_STAGES;
+            if (!bar_wait(&ctrl->full[s], (it / S_STAGES) & 1, &ctrl->abort)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t adesc = smem_desc_sw128(w_tiles + (size_t)s * W_STAGE_BYTES);
+            const uint64_t bdesc = smem_desc_sw128(x_tiles + (size_t)s * X_STAGE_BYTES);
+#pragma unroll
+            for (int k = 0; k < SK / 16; ++k)          // 32 bytes further along K in the swizzled row
+                umma_bf16(tmem_base, adesc + (uint64_t)(k * 32 >> 4), bdesc + (uint64_t)(k * 32 >> 4), IDESC,
+                          (it | k) != 0 ? 1u : 0u);
+            umma_commit(&ctrl->empty[s]);
+        }
+        if (has_work) umma_commit(&ctrl->acc_full);
+    }
+    __syncwarp();
+    pdl_wait();            // nothing is stored before the kernels before this one have finished
+    const bool waited = has_work ? bar_wait(&ctrl->acc_full, 0, &ctrl->abort) : true;
+    const bool ok = __syncthreads_and(waited ? 1 : 0) != 0;       // the same for all threads
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // epilogue: warp w reads TMEM lanes 32 w .. 32 w + 31; lane = feature, column = token
+    const int f = n0 + warp * 32 + lane;
+    const uint32_t tmem_acc = tmem_base + ((uint32_t)(warp * 32) << 16);
+    if (splits == 1) {
+#pragma unroll 1
+        for (int c = 0; c < NT / 16; ++c) {
+            if (c * 16 >= M) break;
+            uint32_t r[16];
+            tmem_ld16(tmem_acc + (uint32_t)(c * 16), r);
+            if (!ok) continue;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (c * 16 + j < M) store_token<EPI, OutT>(y, __uint_as_float(r[j]), c * 16 + j, f, lane, N);
+        }
+    } else {
+        // all products of this CTA are done, so the stages are free: the partial sums go there,
+        // [token][feature of the tile]
+        float* part = reinterpret_cast<float*>(w_tiles);
+#pragma unroll 1
+        for (int c = 0; c < NT / 16; ++c) {
+            if (c * 16 >= M) break;
+            uint32_t r[16];
+            if (has_work) {
+                tmem_ld16(tmem_acc + (uint32_t)(c * 16), r);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (c * 16 + j < M) part[(c * 16 + j) * SF + (int)threadIdx.x] = __uint_as_float(r[j]);
+        }
+        cluster_sync_all();
+#pragma unroll 1
+        for (int t = split; t < M; t += splits) {
+            float v = 0.f;
+            for (int s = 0; s < splits; ++s) v += ld_dsmem(part + t * SF + (int)threadIdx.x, (uint32_t)s);
+            if (ok) store_token<EPI, OutT>(y, v, t, f, lane, N);
+        }
+        cluster_sync_all();        // nobody leaves while its shared memory may still be read
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 2) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+int g_target_ctas = 0;      // 0: 1.3 times the number of SMs
+
+template <int NT, int EPI, typename OutT>
+int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, cudaStream_t stream) {
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, W, N, K, SF) || !make_map(&map_x, x, M, K, NT)) return RLIS_ERR_UNSUPPORTED;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(stream_gemm_kernel<NT, EPI, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)stream_smem_bytes<NT>());
+        cudaFuncSetAttribute(stream_gemm_kernel<NT, EPI, OutT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        attr_done = true;
+    }
+    const int tiles = (N + SF - 1) / SF, k_blocks = (K + SK - 1) / SK;
+    int target = g_target_ctas;
+    if (target <= 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        target = sms + sms * 3 / 10;
+    }
+    // splits (a power of two, the cluster's size) from N and K alone: enough CTAs for the SMs, at
+    // least two stages of k each
+    int splits = 1;
+    while (splits < MAX_SPLITS && tiles * splits < target && k_blocks >= 4 * splits) splits *= 2;
+    const int per = (k_blocks + splits - 1) / splits;
+    rlis_launch_cluster(stream_gemm_kernel<NT, EPI, OutT>, dim3((unsigned)tiles, (unsigned)splits), S_THREADS,
+                        stream_smem_bytes<NT>(), stream, dim3(1, (unsigned)splits, 1), map_w, map_x, (OutT*)y, M, N, K,
+                        per);
+    return RLIS_LAUNCH_CHECK();
+}
+
+template <int NT>
+int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, int out_dtype, int epilogue,
+                    cudaStream_t stream) {
+    if (epilogue == 0 && out_dtype == RLIS_BF16) return launch_stream<NT, 0, bf16>(x, W, y, M, N, K, stream);
+    if (epilogue == 0 && out_dtype == RLIS_F32) return launch_stream<NT, 0, float>(x, W, y, M, N, K, stream);
+    if (epilogue == 1 && out_dtype == RLIS_BF16) return launch_stream<NT, 1, bf16>(x, W, y, M, N, K, stream);
+    return RLIS_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+extern "C" int rlis_stream_gemm_error(void) { return tc::read_error_word(); }
+
+// About how many CTAs a launch is cut into (0: 1.3 times the SMs).  For measurements.
+extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }
+
+// out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (SwiGLU, rows of W interleaved
+// gate/up in blocks of 4, N a multiple of 8): y [M, N / 2].  M up to 128; K a multiple of 8;
+// x and W 16-byte aligned.
+extern "C" int rlis_stream_gemm_bf16(const void* x, const void* W, void* y, int M, int N, int K,
+                                     int out_dtype, int epilogue, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 128 || K <= 0 || (K & 7) != 0) return RLIS_ERR_UNSUPPORTED;
+    if (epilogue == 1 && (N & 7) != 0) return RLIS_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(W) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+        return RLIS_ERR_UNSUPPORTED;
+    if (M <= 16) return dispatch_stream<16>(x, W, y, M, N, K, out_dtype, epilogue, stream);
+    if (M <= 32) return dispatch_stream<32>(x, W, y, M, N, K, out_dtype, epilogue, stream);
+    if (M <= 64) return dispatch_stream<64>(x, W, y, M, N, K, out_dtype, epilogue, stream);
+    return dispatch_stream<128>(x, W, y, M, N, K, out_dtype, epilogue, stream);
+}

@@ -123,23 +123,23 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
-SKINNY_MAX_ROWS = 16
-SKINNY_MAX_FEATURES = 32768     # above this (the LM head) the library GEMM streams weights faster
+STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
+DECODE_GEMM_ROWS = 16     # up to this many rows `linear` uses it; longer batches go to the library GEMM
 
 
-def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False) -> torch.Tensor:
-    """y = x @ w^T for at most 16 rows of bfloat16 x: the weight-streaming tensor-core kernel of
-    the decode step.  `swiglu4`: w is a gate|up matrix interleaved in blocks of 4 rows and the
-    result is silu(gate) * up, [M, N / 2]."""
+def stream_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False) -> torch.Tensor:
+    """y = x @ w^T for at most 128 rows of bfloat16 x: the decode step's weight-streaming product on
+    the tcgen05 tensor cores (TMA-fed, weights as the M side, k split over CTAs).  `swiglu4`: w is a
+    gate|up matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, [M, N / 2]."""
     M, K = x.shape
     N = w.shape[0]
     _req(x, "x", torch.bfloat16)
     _req(w, "w", torch.bfloat16, (N, K))
-    if M > SKINNY_MAX_ROWS or K % 8 or (swiglu4 and N % 8):
-        raise KernelError(f"skinny_gemm: takes up to {SKINNY_MAX_ROWS} rows and K a multiple of 8, got M={M}, K={K}")
+    if M > STREAM_MAX_ROWS or K % 8 or (swiglu4 and N % 8):
+        raise KernelError(f"stream_gemm: takes up to {STREAM_MAX_ROWS} rows and K a multiple of 8, got M={M}, K={K}")
     out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
-    check(lib().rlis_skinny_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
-                                      1 if swiglu4 else 0, _stream()), "skinny_gemm")
+    check(lib().rlis_stream_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
+                                      1 if swiglu4 else 0, _stream()), "stream_gemm")
     _count()
     return out
 
@@ -167,14 +167,14 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> t
 def check_device_errors() -> None:
     """Raises if a bounded wait inside a kernel ever ran out on this device (the kernel then
     finished without its data; results since are not to be trusted).  Synchronises the device."""
-    code = lib().rlis_gemm_tcgen05_error()
+    code = lib().rlis_gemm_tcgen05_error() or lib().rlis_stream_gemm_error()
     if code != 0:
         raise KernelError(f"gemm_tcgen05: a bounded mbarrier wait ran out on the device (code {code})")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
     """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
-    16 rows go to this package's weight-streaming kernel, more to the library GEMM; both
+    16 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
     accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits)."""
     if x.dtype == torch.float32:
         return gemm_f32(x, w)
@@ -182,9 +182,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
         raise KernelError(f"linear: expected matching float32 or bfloat16 operands, got {x.dtype}, {w.dtype}")
     if not x.is_cuda:
         raise KernelError("linear: expected CUDA tensors; there is no CPU path")
-    if (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous()
-            and w.shape[0] < SKINNY_MAX_FEATURES):
-        return skinny_gemm(x, w, out_dtype or torch.bfloat16)
+    if x.shape[0] <= DECODE_GEMM_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+        return stream_gemm(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

@@ -24,7 +24,6 @@ SIGNATURES = {
     "rlis_embedding": [P, P, P, I, I, I, I, P],
     "rlis_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
     "rlis_swiglu": [P, P, I, I, I, I, P],
-    "rlis_skinny_gemm_bf16": [P, P, P, I, I, I, I, I, P],
     "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
@@ -34,6 +33,7 @@ SIGNATURES = {
     "rlis_sample_filtered": [P, P, P, I, I, LL, P],
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
     "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
+    "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
 }
 
 OPTIONAL_SIGNATURES: dict = {}
@@ -60,10 +60,14 @@ def lib():
             fn.restype = c_int
         handle.rlis_gemm_tcgen05_error.argtypes = []
         handle.rlis_gemm_tcgen05_error.restype = c_int
+        handle.rlis_stream_gemm_error.argtypes = []
+        handle.rlis_stream_gemm_error.restype = c_int
+        handle.rlis_stream_gemm_set_target.argtypes = [c_int]
+        handle.rlis_stream_gemm_set_target.restype = None
         handle.rlis_set_pdl.argtypes = [c_int]
         handle.rlis_set_pdl.restype = None
-        if os.environ.get("RLIS_PDL", "0") == "1":      # switch programmatic dependent launch on
-            handle.rlis_set_pdl(1)
+        if os.environ.get("RLIS_PDL", "1") == "0":      # programmatic dependent launch is on unless switched off
+            handle.rlis_set_pdl(0)
         _lib = handle
     return _lib
 

@@ -87,25 +87,39 @@ def test_float32_matrix_product_is_true_float32_and_row_independent(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 8, 8), (8, 3072, 2048), (3, 301, 80), (16, 520, 176), (13, 64, 8200), (5, 1000, 96),
-                                   (8, 20000, 2048), (2, 2048, 8192), (4, 1500, 4104)])
-def test_skinny_product_for_decode_rows(shape):
+                                   (8, 20000, 2048), (2, 2048, 8192), (4, 1500, 4104), (17, 520, 264), (40, 3072, 2048),
+                                   (100, 1096, 1032), (128, 2048, 8192)])
+def test_streaming_product_for_decode_rows(shape):
+    """The tcgen05 weight-streaming kernel: few and many features (one CTA, clusters of 2 to 16
+    splitting k), k that is no multiple of a stage, every row count up to 128."""
     from rust_llm_inference_server_b200 import ops
     M, N, K = shape
     torch.manual_seed(N)
     x, w = torch.randn(M, K).bfloat16(), (torch.randn(N, K) * 0.05).bfloat16()
     want = x.double() @ w.double().t()
-    got32 = ops.skinny_gemm(dev(x), dev(w), torch.float32).cpu()
+    got32 = ops.stream_gemm(dev(x), dev(w), torch.float32).cpu()
     assert (got32.double() - want).abs().max() <= 2e-5 * max(1.0, math.sqrt(K))    # float32 sums of exact products
-    got16 = ops.skinny_gemm(dev(x), dev(w)).cpu()
+    got16 = ops.stream_gemm(dev(x), dev(w)).cpu()
     assert bool(((got16.double() - want).abs() <= 2.0 ** -8 * want.abs() + 1e-4).all())
-    if N < ops.SKINNY_MAX_FEATURES:
+    assert torch.equal(ops.stream_gemm(dev(x), dev(w)).cpu(), got16)                  # the same again: no race in the sums
+    if M <= ops.DECODE_GEMM_ROWS:
         assert torch.equal(ops.linear(dev(x), dev(w)).cpu(), got16)               # `linear` takes this path
-    one = ops.skinny_gemm(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w), torch.float32).cpu()
+    one = ops.stream_gemm(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w), torch.float32).cpu()
     assert torch.equal(one[0], got32[M // 2])                                     # a row ignores its neighbours
+    ops.check_device_errors()
 
 
-@pytest.mark.parametrize("I,K,M", [(8, 16, 2), (176, 80, 7), (8192, 2048, 8)])
-def test_skinny_product_with_gating_and_interleaved_gating_kernel(I, K, M):
+def test_streaming_product_refuses_what_it_cannot_take():
+    from rust_llm_inference_server_b200 import ops
+    from rust_llm_inference_server_b200.ops.library import KernelError
+    with pytest.raises(KernelError, match="rows"):
+        ops.stream_gemm(dev(torch.randn(129, 64).bfloat16()), dev(torch.randn(8, 64).bfloat16()))
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.stream_gemm(dev(torch.randn(2, 36).bfloat16()), dev(torch.randn(8, 36).bfloat16()))
+
+
+@pytest.mark.parametrize("I,K,M", [(8, 16, 2), (176, 80, 7), (8192, 2048, 8), (500, 264, 33), (1024, 512, 128)])
+def test_streaming_product_with_gating_and_interleaved_gating_kernel(I, K, M):
     from rust_llm_inference_server_b200 import ops
     torch.manual_seed(I)
     x = torch.randn(M, K).bfloat16()
@@ -113,7 +127,7 @@ def test_skinny_product_with_gating_and_interleaved_gating_kernel(I, K, M):
     w = torch.stack([g.view(-1, 4, K), u.view(-1, 4, K)], dim=1).reshape(2 * I, K).contiguous()
     gate, up = x.double() @ g.double().t(), x.double() @ u.double().t()
     want = torch.nn.functional.silu(gate) * up
-    got = ops.skinny_gemm(dev(x), dev(w), swiglu4=True).cpu()
+    got = ops.stream_gemm(dev(x), dev(w), swiglu4=True).cpu()
     assert got.shape == (M, I)
     assert bool(((got.double() - want).abs() <= 2.0 ** -7 * want.abs() + 1e-3).all())
     # the two-kernel path of longer batches: product, then the gating kernel on the interleaved layout
