@@ -203,14 +203,13 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
 //   S[heads x 32 keys] = Q K^T      (K rows through ldmatrix, bf16 products, float32 sums)
 //   online softmax in float32 on S * scale
 //   O[heads x D]      += P V        (P rounded to bf16 as the A operand, V through ldmatrix.trans)
-template <int D>
+template <int D, int NSTAGE>
 __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
     float scale, int window, int splits, int* __restrict__ tickets) {
-    pdl_wait_and_trigger();
     __shared__ int s_last;
     constexpr int STRIDE = D + 8;            // elements per padded row
     constexpr int KS = D / 16;               // k-steps of Q K^T
@@ -220,7 +219,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
-    bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 4 * TILE;   // [stage][K|V][32][STRIDE]
+    bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * NSTAGE * 2 * TILE;   // [stage][K|V][32][STRIDE]
 
     const int kvh = blockIdx.x, bi = blockIdx.y, split = blockIdx.z;
     const int row = dec_rows[bi];
@@ -234,19 +233,6 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     const int blk0 = first_blk + split * blk_per_split;
     const int blk1 = min(blk0 + blk_per_split, first_blk + n_blk);
     const size_t head_stride = (size_t)page_size * D;
-
-    // Q as A fragments: row g = head g of the group (rows >= nrep and rows 8..15 are zero)
-    uint32_t qa[KS][4];
-    {
-        const bf16* qrow = q + ((size_t)row * nh + kvh * nrep + (g < nrep ? g : 0)) * D;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qa[ks][0] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
-            qa[ks][1] = 0u;
-            qa[ks][2] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c + 8) : 0u;
-            qa[ks][3] = 0u;
-        }
-    }
 
     // Address arithmetic of the copies is kept short: it runs 2 * CPR times per block and lane and
     // would otherwise outweigh the tensor work.  A page size that is a power of two (the usual
@@ -287,16 +273,53 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[nd][e] = 0.f;
 
+    // NSTAGE - 1 blocks are in flight while one is worked on; a group is committed every turn
+    // (an empty one past the end), so that "all but the newest NSTAGE - 1 groups" is always the
+    // block that is needed.
+    // The step's own inputs (rows, lengths, block tables) were written before its first kernel,
+    // and of this layer's cache the kernel before this one (rotation and cache write) writes only
+    // each request's newest key, ctx - 1.  So blocks that end before that key are requested before
+    // this kernel waits for its predecessor; the block that holds it, and q, after.
     int blk = blk0 + warp;
     int stage = 0;
-    if (blk < blk1) issue(blk, 0);
+    const int newest_blk = (ctx - 1) >> 5;
+    int deferred_from = NSTAGE - 1;
+#pragma unroll
+    for (int i = 0; i < NSTAGE - 1; ++i) {
+        const int b = blk + i * DEC_WARPS;
+        if (b < blk1 && b < newest_blk && deferred_from == NSTAGE - 1) issue(b, i);
+        else if (deferred_from == NSTAGE - 1) deferred_from = i;
+    }
+    pdl_wait_and_trigger();
+#pragma unroll
+    for (int i = 0; i < NSTAGE - 1; ++i) {
+        if (i < deferred_from) continue;
+        const int b = blk + i * DEC_WARPS;
+        if (b < blk1) issue(b, i);
+        else cp_async_commit();
+    }
+
+    // Q as A fragments: row g = head g of the group (rows >= nrep and rows 8..15 are zero)
+    uint32_t qa[KS][4];
+    {
+        const bf16* qrow = q + ((size_t)row * nh + kvh * nrep + (g < nrep ? g : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
+            qa[ks][1] = 0u;
+            qa[ks][2] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c + 8) : 0u;
+            qa[ks][3] = 0u;
+        }
+    }
+
     while (blk < blk1) {
         const int nblk = blk + DEC_WARPS;
-        if (nblk < blk1) {
-            issue(nblk, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        {
+            const int ahead = blk + (NSTAGE - 1) * DEC_WARPS;
+            const int st = stage == 0 ? NSTAGE - 1 : stage - 1;       // the stage worked on last turn
+            if (ahead < blk1) issue(ahead, st);
+            else cp_async_commit();
+            cp_async_wait<NSTAGE - 1>();
         }
         __syncwarp();
         const bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
@@ -367,7 +390,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         }
         __syncwarp();                                   // the stage may be overwritten from here on
         blk = nblk;
-        stage ^= 1;
+        stage = stage + 1 == NSTAGE ? 0 : stage + 1;
     }
 
     // merge the warps through shared memory (the tiles are no longer needed)
@@ -447,8 +470,10 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 constexpr int kMaxTickets = 65536;
 __device__ int g_decode_tickets[kMaxTickets];
 
-template <int D> constexpr size_t decode_mma_smem_bytes() {
-    return (size_t)DEC_WARPS * 4 * 32 * (D + 8) * sizeof(bf16);
+int g_decode_stages = 0;     // 0: chosen from the grid; 2..4 for measurements (rlis_attention_decode_set_stages)
+
+template <int D, int NSTAGE> constexpr size_t decode_mma_smem_bytes() {
+    return (size_t)DEC_WARPS * NSTAGE * 2 * 32 * (D + 8) * sizeof(bf16);
 }
 
 // Merges the splits: big = max m over non-empty splits, w = exp(m - big),
@@ -483,6 +508,8 @@ size_t decode_smem_bytes(int nrep, int d) {
 }  // namespace
 
 // Floats of scratch that `rlis_attention_decode` needs for these sizes (0 when splits == 1).
+extern "C" void rlis_attention_decode_set_stages(int stages) { g_decode_stages = stages; }
+
 extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, int d, int splits) {
     return splits > 1 ? (long long)n_decode * nh * splits * (d + 2) : 0;
 }
@@ -517,26 +544,35 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
             }
         }
         merged = tickets != nullptr;
-        static bool attr_done[2] = {false, false};
+        // Stages of K/V a warp keeps: what shared memory allows for the CTAs to be resident together
+        // (bytes in flight an SM are what the kernel's rate is made of; see the file's head).
+        int sms = 148, dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long ctas = (long long)grid.x * grid.y * grid.z;
+        int stages = g_decode_stages;
+        if (stages == 0) stages = ctas <= sms ? 4 : (ctas <= 2 * sms ? 3 : 2);
+        if (d == 128 && stages > 3) stages = 3;               // 4 stages of 128-wide rows do not fit
+#define LAUNCH_MMA(DD, NS)                                                                             \
+    do {                                                                                               \
+        static bool attr_done = false;                                                                 \
+        if (!attr_done) {                                                                              \
+            cudaFuncSetAttribute(attn_decode_mma_kernel<DD, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)decode_mma_smem_bytes<DD, NS>());                                \
+            attr_done = true;                                                                          \
+        }                                                                                              \
+        rlis_launch(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), stream, \
+            (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
+            ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets); \
+    } while (0)
         if (d == 64) {
-            if (!attr_done[0]) {
-                cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)decode_mma_smem_bytes<64>());
-                attr_done[0] = true;
-            }
-            rlis_launch(attn_decode_mma_kernel<64>, grid, DEC_THREADS, decode_mma_smem_bytes<64>(), stream, 
-                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
-                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets);
+            if (stages >= 4) LAUNCH_MMA(64, 4);
+            else if (stages == 3) LAUNCH_MMA(64, 3);
+            else LAUNCH_MMA(64, 2);
         } else {
-            if (!attr_done[1]) {
-                cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)decode_mma_smem_bytes<128>());
-                attr_done[1] = true;
-            }
-            rlis_launch(attn_decode_mma_kernel<128>, grid, DEC_THREADS, decode_mma_smem_bytes<128>(), stream, 
-                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs,
-                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets);
+            if (stages >= 3) LAUNCH_MMA(128, 3);
+            else LAUNCH_MMA(128, 2);
         }
+#undef LAUNCH_MMA
         launched = true;
     }
 #define LAUNCH(N)                                                                                   \

@@ -72,7 +72,8 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
                                       const int* __restrict__ positions, const int* __restrict__ slots,
                                       const float* __restrict__ inv_freq, int nh, int nkv, int d,
                                       int page_size) {
-    pdl_wait_and_trigger();
+    // Positions and slots are the step's own inputs, written before its first kernel: the angles
+    // are ready by the time the projection before this kernel has finished.
     constexpr int VN = Vec16<T>::N;
     extern __shared__ float cs[];
     const int t = blockIdx.x;
@@ -80,15 +81,16 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
     float* cc = cs;
     float* sn = cs + half;
     const float pos = (float)positions[t];
+    const int slot = slots != nullptr ? slots[t] : -1;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         float s_ = 0.f, c_ = 1.f;
         if (inv_freq != nullptr) sincosf(pos * inv_freq[j], &s_, &c_);
         cc[j] = c_;
         sn[j] = s_;
     }
+    pdl_wait_and_trigger();
     __syncthreads();
     const T* x = qkv + (size_t)t * (nh + 2 * nkv) * d;
-    const int slot = slots != nullptr ? slots[t] : -1;
     const long long page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot % page_size : 0;
     const int cph = half / VN;                       // vectors per half head
