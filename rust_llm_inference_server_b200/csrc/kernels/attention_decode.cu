@@ -203,14 +203,29 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
 //   S[heads x 32 keys] = Q K^T      (K rows through ldmatrix, bf16 products, float32 sums)
 //   online softmax in float32 on S * scale
 //   O[heads x D]      += P V        (P rounded to bf16 as the A operand, V through ldmatrix.trans)
+// With `qkv` set the kernel does the work of the rotation kernel too, for steps that decode only:
+// q comes straight from the q|k|v projection and is rotated as it is loaded; the warp that meets
+// the block with the request's newest key rotates that key, puts key and value into its tile and
+// into the cache (slots == nullptr: the layer reads another layer's cache and stores nothing).
+// The arithmetic is that of rope_cache.cu, bit for bit.
+struct DecodeQkv {
+    const bf16* qkv;            // [tokens, (nh + 2 nkv) d], or nullptr: q is rotated and the cache is written already
+    const int* positions;       // [tokens]
+    const int* slots;           // [tokens] page * page_size + offset of the token's key, or nullptr
+    const float* inv_freq;      // [d / 2], or nullptr: no rotation
+    bf16* k_cache;              // the same arrays as the kernel reads, for the newest key
+    bf16* v_cache;
+};
+
 template <int D, int NSTAGE>
 __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    const bf16* __restrict__ q, const bf16* k_cache, const bf16* v_cache,
     bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
-    float scale, int window, int splits, int* __restrict__ tickets) {
+    float scale, int window, int splits, int* __restrict__ tickets, DecodeQkv fz) {
     __shared__ int s_last;
+    __shared__ float s_cos[D / 2], s_sin[D / 2];
     constexpr int STRIDE = D + 8;            // elements per padded row
     constexpr int KS = D / 16;               // k-steps of Q K^T
     constexpr int ND = D / 8;                // n-tiles of P V
@@ -283,6 +298,16 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     int blk = blk0 + warp;
     int stage = 0;
     const int newest_blk = (ctx - 1) >> 5;
+    const bool fused = fz.qkv != nullptr;
+    if (fused) {                // the angles of this token: positions are an input of the step
+        const float pos = (float)fz.positions[row];
+        for (int j = threadIdx.x; j < D / 2; j += DEC_THREADS) {
+            float sn = 0.f, cn = 1.f;
+            if (fz.inv_freq != nullptr) sincosf(pos * fz.inv_freq[j], &sn, &cn);
+            s_cos[j] = cn;
+            s_sin[j] = sn;
+        }
+    }
     int deferred_from = NSTAGE - 1;
 #pragma unroll
     for (int i = 0; i < NSTAGE - 1; ++i) {
@@ -301,13 +326,33 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 
     // Q as A fragments: row g = head g of the group (rows >= nrep and rows 8..15 are zero)
     uint32_t qa[KS][4];
-    {
+    if (!fused) {
         const bf16* qrow = q + ((size_t)row * nh + kvh * nrep + (g < nrep ? g : 0)) * D;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             qa[ks][0] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c) : 0u;
             qa[ks][1] = 0u;
             qa[ks][2] = g < nrep ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c + 8) : 0u;
+            qa[ks][3] = 0u;
+        }
+    } else {
+        __syncthreads();        // the angles
+        const bf16* qrow = fz.qkv + (size_t)row * (nh + 2 * nkv) * D + (size_t)(kvh * nrep + (g < nrep ? g : 0)) * D;
+        auto rotated = [&](int d0) -> uint32_t {      // dims d0, d0 + 1 of the rotated head, packed
+            const bool first = d0 < D / 2;
+            const int j = first ? d0 : d0 - D / 2;
+            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(qrow + j);
+            const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(qrow + j + D / 2);
+            const float a0 = __bfloat162float(lo.x), a1 = __bfloat162float(lo.y);
+            const float b0 = __bfloat162float(hi.x), b1 = __bfloat162float(hi.y);
+            return first ? pack_bf16(rope_first(a0, b0, s_cos[j], s_sin[j]), rope_first(a1, b1, s_cos[j + 1], s_sin[j + 1]))
+                         : pack_bf16(rope_second(a0, b0, s_cos[j], s_sin[j]), rope_second(a1, b1, s_cos[j + 1], s_sin[j + 1]));
+        };
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = g < nrep ? rotated(ks * 16 + 2 * c) : 0u;
+            qa[ks][1] = 0u;
+            qa[ks][2] = g < nrep ? rotated(ks * 16 + 2 * c + 8) : 0u;
             qa[ks][3] = 0u;
         }
     }
@@ -324,6 +369,33 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         __syncwarp();
         const bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
         const bf16* vs_ = ks_ + TILE;
+        if (fused && fz.slots != nullptr && blk == newest_blk) {
+            // the request's newest key and value: from the projection into this tile and into the cache
+            const int r = (ctx - 1) & 31;
+            const bf16* krow = fz.qkv + (size_t)row * (nh + 2 * nkv) * D + (size_t)(nh + kvh) * D;
+            const bf16* vrow = krow + (size_t)nkv * D;
+            const int slot = fz.slots[row];
+            if (slot >= 0) {
+            const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (size_t)(slot % page_size)) * D;
+            bf16* kt = const_cast<bf16*>(ks_) + r * STRIDE;
+            bf16* vt = const_cast<bf16*>(vs_) + r * STRIDE;
+            for (int j = lane; j < D / 2; j += 32) {
+                const float a = __bfloat162float(krow[j]), b = __bfloat162float(krow[j + D / 2]);
+                const bf16 k1 = from_f<bf16>(rope_first(a, b, s_cos[j], s_sin[j]));
+                const bf16 k2 = from_f<bf16>(rope_second(a, b, s_cos[j], s_sin[j]));
+                const bf16 v1 = vrow[j], v2 = vrow[j + D / 2];
+                kt[j] = k1;
+                kt[j + D / 2] = k2;
+                vt[j] = v1;
+                vt[j + D / 2] = v2;
+                fz.k_cache[at + j] = k1;
+                fz.k_cache[at + j + D / 2] = k2;
+                fz.v_cache[at + j] = v1;
+                fz.v_cache[at + j + D / 2] = v2;
+            }
+            }
+            __syncwarp();
+        }
 
         float sacc[4][4];
 #pragma unroll
@@ -514,18 +586,18 @@ extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, 
     return splits > 1 ? (long long)n_decode * nh * splits * (d + 2) : 0;
 }
 
-extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const void* v_cache,
-                                     void* out, float* partial, const int* dec_rows,
-                                     const int* dec_seqs, const int* ctx_lens,
-                                     const int* block_tables, int max_blocks, int n_decode, int nh,
-                                     int nkv, int d, int page_size, float scale, int window,
-                                     int splits, int dtype, cudaStream_t stream) {
+namespace {
+int decode_launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
+                  const int* dec_rows, const int* dec_seqs, const int* ctx_lens, const int* block_tables,
+                  int max_blocks, int n_decode, int nh, int nkv, int d, int page_size, float scale,
+                  int window, int splits, int dtype, cudaStream_t stream, const DecodeQkv& fz) {
     if (n_decode <= 0) return 0;
     if (dtype != RLIS_BF16 || d % 8 != 0 || d > 256 || d < 8 || nkv <= 0 || nh % nkv != 0 || splits < 1)
         return RLIS_ERR_UNSUPPORTED;
     const int nrep = nh / nkv;
     if (nrep > 8) return RLIS_ERR_UNSUPPORTED;
     if (splits > 1 && partial == nullptr) return RLIS_ERR_UNSUPPORTED;
+    if (fz.qkv != nullptr && d != 64 && d != 128) return RLIS_ERR_UNSUPPORTED;   // only the tensor-core kernel rotates
     dim3 grid(nkv, n_decode, splits);
     const size_t smem = decode_smem_bytes(nrep, d);
     bool launched = false;
@@ -562,7 +634,7 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
         }                                                                                              \
         rlis_launch(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), stream, \
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
-            ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets); \
+            ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz); \
     } while (0)
         if (d == 64) {
             if (stages >= 4) LAUNCH_MMA(64, 4);
@@ -596,6 +668,34 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
     const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
     rlis_launch(attn_decode_combine_kernel, dim3(nh, n_decode), threads, 0, stream, partial, (bf16*)out, dec_rows, nh, d, splits);
     return RLIS_LAUNCH_CHECK();
+}
+}  // namespace
+
+extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                     void* out, float* partial, const int* dec_rows,
+                                     const int* dec_seqs, const int* ctx_lens,
+                                     const int* block_tables, int max_blocks, int n_decode, int nh,
+                                     int nkv, int d, int page_size, float scale, int window,
+                                     int splits, int dtype, cudaStream_t stream) {
+    const DecodeQkv none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    return decode_launch(q, k_cache, v_cache, out, partial, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks,
+                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, none);
+}
+
+// The same for a step that decodes only, straight from the q|k|v projection [tokens, (nh + 2 nkv) d]
+// (head sizes 64 and 128): q and the newest key are rotated inside the kernel (inv_freq == nullptr:
+// no rotation) and the newest key and value are stored at slots[token] (slots == nullptr: nothing
+// is stored and the cache is taken to hold the key already).  ctx_lens counts the newest key.
+extern "C" int rlis_attention_decode_qkv(const void* qkv, const int* positions, const int* slots,
+                                         const float* inv_freq, void* k_cache, void* v_cache, void* out,
+                                         float* partial, const int* dec_rows, const int* dec_seqs,
+                                         const int* ctx_lens, const int* block_tables, int max_blocks,
+                                         int n_decode, int nh, int nkv, int d, int page_size, float scale,
+                                         int window, int splits, int dtype, cudaStream_t stream) {
+    if (qkv == nullptr || positions == nullptr) return RLIS_ERR_UNSUPPORTED;
+    const DecodeQkv fz = {(const bf16*)qkv, positions, slots, inv_freq, (bf16*)k_cache, (bf16*)v_cache};
+    return decode_launch(nullptr, k_cache, v_cache, out, partial, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks,
+                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, fz);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -72,6 +72,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return r;
 }
 
+// Rotate-half of the pair (a, b) = (x[j], x[j + d/2]) by the angle with cosine c and sine s, in
+// float32 with the operations spelled out, so that every kernel that rotates gets the same bits.
+__device__ __forceinline__ float rope_first(float a, float b, float c, float s) {
+    return __fmaf_rn(a, c, -__fmul_rn(b, s));
+}
+__device__ __forceinline__ float rope_second(float a, float b, float c, float s) {
+    return __fmaf_rn(b, c, __fmul_rn(a, s));
+}
+
 #define RLIS_LAUNCH_CHECK() ((int)cudaGetLastError())
 
 // ---- programmatic dependent launch --------------------------------------------------------

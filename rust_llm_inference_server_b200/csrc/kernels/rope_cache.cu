@@ -46,14 +46,14 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
         const float x2 = to_f<T>(x[head * d + j + half]);
         if (head < nh) {
             T* o = q_out + ((size_t)t * nh + head) * d;
-            o[j] = from_f<T>(x1 * c[j] - x2 * s[j]);
-            o[j + half] = from_f<T>(x2 * c[j] + x1 * s[j]);
+            o[j] = from_f<T>(rope_first(x1, x2, c[j], s[j]));
+            o[j + half] = from_f<T>(rope_second(x1, x2, c[j], s[j]));
         } else if (slot >= 0) {
             if (head < nh + nkv) {
                 const int kvh = head - nh;
                 T* o = k_cache + (((size_t)page * nkv + kvh) * page_size + off) * d;
-                o[j] = from_f<T>(x1 * c[j] - x2 * s[j]);
-                o[j + half] = from_f<T>(x2 * c[j] + x1 * s[j]);
+                o[j] = from_f<T>(rope_first(x1, x2, c[j], s[j]));
+                o[j + half] = from_f<T>(rope_second(x1, x2, c[j], s[j]));
             } else {
                 const int kvh = head - nh - nkv;
                 T* o = v_cache + (((size_t)page * nkv + kvh) * page_size + off) * d;
@@ -121,8 +121,8 @@ __global__ void rope_cache_vec_kernel(const T* __restrict__ qkv, T* __restrict__
 #pragma unroll
         for (int e = 0; e < VN; ++e) {
             const float c_ = cc[j0 + e], s_ = sn[j0 + e];
-            p1[e] = from_f<T>(a[e] * c_ - b[e] * s_);
-            p2[e] = from_f<T>(b[e] * c_ + a[e] * s_);
+            p1[e] = from_f<T>(rope_first(a[e], b[e], c_, s_));
+            p2[e] = from_f<T>(rope_second(a[e], b[e], c_, s_));
         }
         *reinterpret_cast<uint4*>(dst + j0) = o1;
         *reinterpret_cast<uint4*>(dst + half + j0) = o2;

@@ -301,6 +301,46 @@ def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, blo
     return out
 
 
+def decode_attention_takes_qkv(dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """Whether `attention_decode_from_qkv` exists for these sizes (the tensor-core decode kernel)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv_heads == 0
+            and n_heads // n_kv_heads <= 8)
+
+
+def attention_decode_from_qkv(qkv, k_cache, v_cache, out, step, group: int, inv_freq, store: bool,
+                              n_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                              scale: float, window: int = 0) -> torch.Tensor:
+    """Decode attention of a step of single tokens straight from the q|k|v projection
+    [T, (nh + 2 nkv) d]: rotates q and each request's newest key (`inv_freq` float32 [d / 2], None:
+    no rotation) inside the attention kernel, which also stores the newest key and value at the
+    step's slots (`store` False: the layer reads another layer's cache)."""
+    T = qkv.shape[0]
+    n = step.n_decode
+    _req(qkv, "qkv", torch.bfloat16, (T, (n_heads + 2 * n_kv_heads) * head_dim))
+    _req(out, "out", torch.bfloat16, (T, n_heads * head_dim))
+    _req(k_cache, "k_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    _req(v_cache, "v_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
+    if not decode_attention_takes_qkv(qkv.dtype, n_heads, n_kv_heads, head_dim):
+        raise KernelError(f"decode attention from q|k|v: head size {head_dim} / {n_heads}:{n_kv_heads} heads is not taken")
+    if inv_freq is not None:
+        _req(inv_freq, "inv_freq", torch.float32, (head_dim // 2,))
+    slots = step.slots[group] if store else None
+    tables = step.block_tables[group]
+    splits = decode_splits(n, n_kv_heads, step.max_decode_ctx)
+    scratch = None
+    if splits > 1:
+        scratch = step.buffer("attn_partial", (n * n_heads * splits * (head_dim + 2),), torch.float32)
+    check(lib().rlis_attention_decode_qkv(
+        qkv.data_ptr(), step.positions.data_ptr(), slots.data_ptr() if slots is not None else None,
+        inv_freq.data_ptr() if inv_freq is not None else None, k_cache.data_ptr(), v_cache.data_ptr(),
+        out.data_ptr(), scratch.data_ptr() if splits > 1 else None, step.dec_rows.data_ptr(),
+        step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n, n_heads,
+        n_kv_heads, head_dim, page_size, float(scale), int(window), int(splits), _code(qkv.dtype), _stream()),
+        "attention_decode_qkv")
+    _count()
+    return out
+
+
 def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,
                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                       window: int = 0) -> torch.Tensor:

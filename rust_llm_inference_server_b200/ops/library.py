@@ -28,6 +28,7 @@ SIGNATURES = {
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
+    "rlis_attention_decode_qkv": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
     "rlis_sample_filtered": [P, P, P, I, I, LL, P],

@@ -54,10 +54,19 @@ class GQAAttention(Mixer):
         s = self.spec
         T = x.shape[0]
         qkv = ops.linear(x, self.w_qkv)
+        o = step.buffer("attn_o", (T, s.n_heads * s.head_dim), self.dtype)
+        if step.all_decode and ops.decode_attention_takes_qkv(qkv.dtype, s.n_heads, s.n_kv_heads, s.head_dim):
+            table = self.position.rotate_half_table()
+            if table is not NotImplemented:
+                # a step of single tokens: the attention kernel rotates q and the newest key and
+                # stores that key itself, one kernel fewer a layer
+                ops.attention_decode_from_qkv(qkv, cache.k, cache.v, o, step, cache.group, table, writes_cache,
+                                              s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size,
+                                              self.scale, self.window)
+                return ops.linear(o, self.w_o)
         q = step.buffer("attn_q", (T, s.n_heads * s.head_dim), self.dtype)
         self.position.encode_and_store(qkv, q, cache, step, s.n_heads, s.n_kv_heads, s.head_dim,
                                        store=writes_cache)
-        o = step.buffer("attn_o", (T, s.n_heads * s.head_dim), self.dtype)
         ops.attention(q, cache.k, cache.v, o, step, cache.group, s.n_heads, s.n_kv_heads,
                       s.head_dim, cache.page_size, self.scale, self.window)
         return ops.linear(o, self.w_o)

@@ -102,6 +102,13 @@ class PositionEncoding(Part):
                          n_kv_heads: int, head_dim: int, store: bool) -> None:
         raise NotImplementedError
 
+    def rotate_half_table(self):
+        """For mixers whose decode kernel can encode positions itself: the float32 inverse
+        frequencies [head_dim / 2] of a rotate-half encoding, None for "no encoding", or
+        NotImplemented (the default) when the encoding is anything else; the mixer then calls
+        `encode_and_store` as for every other step."""
+        return NotImplemented
+
 
 _MIXERS: dict[str, Callable] = {}
 _FEED_FORWARDS: dict[str, Callable] = {}

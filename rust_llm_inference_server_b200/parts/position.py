@@ -51,6 +51,9 @@ class Rope(PositionEncoding):
                        self.inv_freq, n_heads, n_kv_heads, head_dim,
                        cache.page_size if cache is not None else 1)
 
+    def rotate_half_table(self):
+        return self.inv_freq
+
 
 class NoPosition(PositionEncoding):
     """No encoding: q is copied out and k, v are stored as they are."""
@@ -64,6 +67,9 @@ class NoPosition(PositionEncoding):
                        cache.v if slots is not None else None, step.positions, slots,
                        None, n_heads, n_kv_heads, head_dim,
                        cache.page_size if cache is not None else 1)
+
+    def rotate_half_table(self):
+        return None
 
 
 register_position("rope", Rope)

@@ -391,6 +391,63 @@ def test_decode_attention_far_key_and_window():
             assert ((got[0] - 7.0).abs().max() < 0.05) == seen, (key, window, splits)
 
 
+@pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((6, 3, 128), 16), ((8, 8, 64), 8), ((4, 1, 128), 32)])
+@pytest.mark.parametrize("rotate,store,window", [(True, True, 0), (False, True, 0), (True, False, 0), (True, True, 70)])
+def test_decode_attention_from_the_projection_equals_rotation_then_attention(geom, ps, rotate, store, window):
+    """A step of single tokens: the kernel that rotates q and the newest key itself and stores that
+    key gives the bits of the two-kernel path, in the output and in the cache.  Contexts that end
+    at a page's and at a block's first and last slot, one token long, and long."""
+    from types import SimpleNamespace
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d = geom
+    lens = [1, 2, 31, 32, 33, 64, 65, 700, 2049, ps, ps + 1, 3 * ps - 1]
+    B = len(lens)
+    g = torch.Generator().manual_seed(d + ps + window)
+    n_pages = sum(-(-n // ps) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_blocks = max(-(-n // ps) for n in lens)
+    tables = torch.zeros(B, max_blocks, dtype=torch.int32)
+    slots = torch.zeros(B, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for i in range(-(-n // ps)):
+            tables[b, i] = perm.pop()
+        slots[b] = tables[b, (n - 1) // ps] * ps + (n - 1) % ps
+    kc = (torch.randn(n_pages, nkv, ps, d, generator=g) * 0.7).bfloat16()
+    vc = (torch.randn(n_pages, nkv, ps, d, generator=g) * 0.7).bfloat16()
+    qkv = (torch.randn(B, (nh + 2 * nkv) * d, generator=g) * 0.7).bfloat16()
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    inv_freq = dev((1.0 / 10000.0 ** (torch.arange(0, d, 2).float() / d)).contiguous()) if rotate else None
+    ctx = dev(torch.tensor(lens, dtype=torch.int32))
+    ar = dev(torch.arange(B, dtype=torch.int32))
+    scale = 1 / math.sqrt(d)
+    bufs = {}
+
+    def buffer(name, shape, dtype):
+        return bufs.setdefault((name, shape), torch.empty(shape, dtype=dtype, device="cuda"))
+
+    for max_ctx in (max(lens), 4 * 128):          # many splits and few
+        step = SimpleNamespace(n_decode=B, slots={0: dev(slots)}, block_tables={0: dev(tables)}, max_decode_ctx=max_ctx,
+                               positions=dev(pos), dec_rows=ar, dec_seqs=ar, ctx_lens=ctx, buffer=buffer)
+        # two kernels
+        k1, v1 = dev(kc).clone(), dev(vc).clone()
+        q1 = torch.empty(B, nh * d, dtype=torch.bfloat16, device="cuda")
+        ops.rope_cache(dev(qkv), q1, k1 if store else None, v1 if store else None, step.positions,
+                       step.slots[0] if store else None, inv_freq, nh, nkv, d, ps)
+        out1 = torch.zeros(B, nh * d, dtype=torch.bfloat16, device="cuda")
+        splits = ops.decode_splits(B, nkv, max_ctx)
+        scratch = torch.empty(B * nh * splits * (d + 2), dtype=torch.float32, device="cuda")
+        ops.attention_decode(q1, k1, v1, out1, ar, ar, ctx, step.block_tables[0], nh, nkv, d, ps, scale, window,
+                             splits, scratch)
+        # one kernel
+        k2, v2 = dev(kc).clone(), dev(vc).clone()
+        out2 = torch.zeros(B, nh * d, dtype=torch.bfloat16, device="cuda")
+        ops.attention_decode_from_qkv(dev(qkv), k2, v2, out2, step, 0, inv_freq, store, nh, nkv, d, ps, scale, window)
+        assert torch.equal(out1, out2)
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)
+        if store:
+            assert not torch.equal(k2, dev(kc))                  # the newest keys did arrive
+
+
 def test_sample_rows_equals_the_plain_sampler():
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(0)

@@ -43,6 +43,7 @@ class FakeStep:
         self.dec_seqs = i32(dec) if dec else None
         self.dec_rows = i32([self.q_starts[b] for b in dec]) if dec else None
         self.max_decode_ctx = max([starts[b] + 1 for b in dec], default=0)
+        self.all_decode = max(lens) == 1
         rows = [r for b, n in enumerate(lens) if n > 1 for r in range(self.q_starts[b], self.q_starts[b] + n)]
         self.n_prefill_tokens = len(rows)
         self.prefill_rows = i32(rows) if (dec and rows) else None
@@ -137,6 +138,53 @@ def test_attention_part_over_two_steps(dtype, window, rotate):
 
     for got, x in ((got_a, xa), (got_b, xb)):
         err = (got - plain(x.float())).abs().max()
+        assert err <= tol(dtype) * 2, err
+
+
+@pytest.mark.parametrize("window", [None, 9])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_attention_part_in_steps_of_single_tokens(window, rotate):
+    """Head size 64 in bfloat16: steps of single tokens take the kernel that rotates and stores
+    the newest key itself.  A prompt in one step, then three steps of one token for each of two
+    requests; the outputs equal plain attention over the whole sequences."""
+    from rust_llm_inference_server_b200.parts import GQAAttentionSpec, LayerCache, NoPositionSpec, RopeSpec, build_mixer
+    torch.manual_seed(2)
+    dtype = torch.bfloat16
+    H, nh, nkv, d, ps = 96, 4, 2, 64, 8
+    cfg = {"head_dim": d, "rope_theta": 5000.0, "hidden_size": H, "num_attention_heads": nh, "num_key_value_heads": nkv}
+    w = {"q": torch.randn(nh * d, H) * 0.2, "k": torch.randn(nkv * d, H) * 0.2, "v": torch.randn(nkv * d, H) * 0.2,
+         "o": torch.randn(H, nh * d) * 0.1}     # 256 inputs: outputs of the size the other part tests have
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    spec = GQAAttentionSpec(H, nh, nkv, d, "q", "k", "v", "o",
+                            position=RopeSpec(d, 5000.0, None) if rotate else NoPositionSpec(), window=window)
+    att = build_mixer(spec, dtype, "cuda")
+    att.load(DictSource(w, dtype))
+    n_a, n_b, n_dec = 15, 6, 3
+    xa, xb = torch.randn(n_a + n_dec, H).to(dtype), torch.randn(n_b + n_dec, H).to(dtype)
+    pool = torch.zeros(2, 9, nkv, ps, d, dtype=dtype, device="cuda")
+    cache = LayerCache(pool[0], pool[1], 0, ps)
+    tables = [[7, 2, 5], [0, 8]]
+    o = att.forward(torch.cat([xa[:n_a], xb[:n_b]]).cuda(), FakeStep([0, 0], [n_a, n_b], ps, tables), cache, None)
+    got_a, got_b = [o[:n_a]], [o[n_a:]]
+    for i in range(n_dec):
+        step = FakeStep([n_a + i, n_b + i], [1, 1], ps, tables)
+        assert step.all_decode
+        o = att.forward(torch.stack([xa[n_a + i], xb[n_b + i]]).cuda(), step, cache, None)
+        got_a.append(o[:1])
+        got_b.append(o[1:])
+
+    def plain(x):
+        n = x.shape[0]
+        q = P.linear(x, w["q"]).view(n, nh, d).bfloat16().float()
+        k = P.linear(x, w["k"]).view(n, nkv, d).bfloat16().float()
+        v = P.linear(x, w["v"]).view(n, nkv, d).bfloat16().float()
+        if rotate:
+            cos, sin = P.rope_tables(P.inv_freqs(cfg), torch.arange(n))
+            q, k = P.apply_rope(q, cos, sin), P.apply_rope(k, cos, sin)
+        return P.linear(P.causal_attention(q, k, v, 0, window=window).reshape(n, nh * d), w["o"])
+
+    for got, x in ((got_a, xa), (got_b, xb)):
+        err = (torch.cat(got).float().cpu() - plain(x.float())).abs().max()
         assert err <= tol(dtype) * 2, err
 
 
