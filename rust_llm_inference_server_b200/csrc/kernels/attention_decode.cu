@@ -217,15 +217,19 @@ struct DecodeQkv {
     bf16* v_cache;
 };
 
+constexpr int DEC_TABLE_SLOTS = 1024;     // block-table entries of a CTA kept in shared memory
+
+
 template <int D, int NSTAGE>
 __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     const bf16* __restrict__ q, const bf16* k_cache, const bf16* v_cache,
     bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int nrep, int page_size,
-    float scale, int window, int splits, int* __restrict__ tickets, DecodeQkv fz) {
+    float scale, int window, int splits, int* __restrict__ tickets, DecodeQkv fz, int cluster_merge) {
     __shared__ int s_last;
     __shared__ float s_cos[D / 2], s_sin[D / 2];
+    __shared__ int s_table[DEC_TABLE_SLOTS];
     constexpr int STRIDE = D + 8;            // elements per padded row
     constexpr int KS = D / 16;               // k-steps of Q K^T
     constexpr int ND = D / 8;                // n-tiles of P V
@@ -256,6 +260,16 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     const size_t page_stride = (size_t)nkv * head_stride;
     const bf16* kbase = k_cache + (size_t)kvh * head_stride;
     const bf16* vbase = v_cache + (size_t)kvh * head_stride;
+    // This CTA's part of the block table, fetched once (it is an input of the step): a lookup in
+    // global memory per copy would sit on the path of every request for keys.
+    const int page0 = page_shift >= 0 ? (blk0 << 5) >> page_shift : (blk0 << 5) / page_size;
+    const int key_end = min(blk1 << 5, ctx);
+    const int n_pages = key_end > (blk0 << 5) ? (page_shift >= 0 ? (key_end - 1) >> page_shift : (key_end - 1) / page_size) - page0 + 1 : 0;
+    const bool table_in_smem = n_pages <= DEC_TABLE_SLOTS;
+    if (table_in_smem) {
+        for (int i = threadIdx.x; i < n_pages; i += DEC_THREADS) s_table[i] = table[page0 + i];
+        __syncthreads();
+    }
     const int key_in0 = lane / CPR, c16 = lane % CPR;       // chunk i of a lane: key_in0 + i * (32 / CPR)
     const uint32_t sm_off0 = (uint32_t)(key_in0 * STRIDE + c16 * 8);
     auto issue = [&](int blk, int stage) {
@@ -270,7 +284,8 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             if (valid) {
                 const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
                 const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
-                off = (size_t)table[pi] * page_stride + (uint32_t)(in_page * D + c16 * 8);
+                const int page = table_in_smem ? s_table[pi - page0] : table[pi];
+                off = (size_t)page * page_stride + (uint32_t)(in_page * D + c16 * 8);
             }
             const uint32_t so = sm_off0 + (uint32_t)(i * (32 / CPR) * STRIDE);
             cp_async16(ks_ + so, kbase + off, valid);
@@ -499,6 +514,13 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         const int head = kvh * nrep + h;
         if (splits == 1) {
             out[((size_t)row * nh + head) * D + j] = from_f<bf16>(a / lsum);
+        } else if (cluster_merge) {
+            float* cl = ml + DEC_WARPS * nrep * 2;          // [nrep][D], then m [nrep], l [nrep]
+            cl[i] = a;
+            if (j == 0) {
+                cl[nrep * D + h] = big * 0.6931471805599453f;
+                cl[nrep * D + nrep + h] = lsum;
+            }
         } else {
             float* pr = partial + (((size_t)bi * nh + head) * splits + split) * (D + 2);
             pr[j] = a;
@@ -507,6 +529,39 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
                 pr[D + 1] = lsum;
             }
         }
+    }
+    if (splits > 1 && cluster_merge) {
+        // The splits of a (request, kv head) are the CTAs of a cluster: each has left its sums in
+        // its own shared memory, and after the barrier CTA r merges a slice of the outputs from all
+        // of them through distributed shared memory, in split order.  No trip through global memory.
+        const float* cl = ml + DEC_WARPS * nrep * 2;
+        cluster_sync_all();
+        const int total = nrep * D, per = (total + splits - 1) / splits;
+        const int i1 = min(total, (split + 1) * per);
+        for (int i = split * per + threadIdx.x; i < i1; i += DEC_THREADS) {
+            const int h = i / D, j = i - h * D;
+            float mv[8], av[8], lv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = u < splits;
+                mv[u] = in ? ld_dsmem(cl + nrep * D + h, (uint32_t)u) : -INFINITY;
+                av[u] = in ? ld_dsmem(cl + i, (uint32_t)u) : 0.f;
+                lv[u] = in ? ld_dsmem(cl + nrep * D + nrep + h, (uint32_t)u) : 0.f;
+            }
+            float big = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) big = fmaxf(big, mv[u]);
+            float a = 0.f, lsum = 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float wgt = mv[u] == -INFINITY ? 0.f : expf(mv[u] - big);
+                a += av[u] * wgt;
+                lsum += lv[u] * wgt;
+            }
+            out[((size_t)row * nh + kvh * nrep + h) * D + j] = from_f<bf16>(a / lsum);
+        }
+        cluster_sync_all();        // nobody leaves while its shared memory may still be read
+        return;
     }
     if (splits > 1 && tickets != nullptr) {
         // The CTA that takes the last ticket of its (request, kv head) merges the splits, in split
@@ -521,15 +576,35 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
                 const int h = i / D, j = i - h * D;
                 const int head = kvh * nrep + h;
                 const float* pr = partial + ((size_t)bi * nh + head) * splits * (D + 2);
-                float big = -INFINITY;
-                for (int sp = 0; sp < splits; ++sp) big = fmaxf(big, __ldcg(pr + (size_t)sp * (D + 2) + D));
-                float a = 0.f, lsum = 0.f;
-                for (int sp = 0; sp < splits; ++sp) {
-                    const float* r = pr + (size_t)sp * (D + 2);
-                    const float mw = __ldcg(r + D);
-                    const float wgt = mw == -INFINITY ? 0.f : expf(mw - big);
-                    a += __ldcg(r + j) * wgt;
-                    lsum += __ldcg(r + D + 1) * wgt;
+                // Pieces of 8 splits: all loads of a piece are issued before any is used (one trip
+                // to L2 a piece), and the pieces are folded with the running maximum.  With up to
+                // 8 splits this is the plain merge: big = max m, sums of acc and l times exp(m - big).
+                constexpr int MU = 8;
+                float big = -INFINITY, a = 0.f, lsum = 0.f;
+                for (int sp0 = 0; sp0 < splits; sp0 += MU) {
+                    float mv[MU], av[MU], lv[MU];
+#pragma unroll
+                    for (int u = 0; u < MU; ++u) {
+                        const bool in = sp0 + u < splits;
+                        const float* r = pr + (size_t)(in ? sp0 + u : 0) * (D + 2);
+                        mv[u] = in ? __ldcg(r + D) : -INFINITY;
+                        av[u] = in ? __ldcg(r + j) : 0.f;
+                        lv[u] = in ? __ldcg(r + D + 1) : 0.f;
+                    }
+                    float nb = big;
+#pragma unroll
+                    for (int u = 0; u < MU; ++u) nb = fmaxf(nb, mv[u]);
+                    if (nb == -INFINITY) continue;              // no split of this piece held a key
+                    const float keep = big == -INFINITY ? 0.f : expf(big - nb);
+                    a *= keep;
+                    lsum *= keep;
+#pragma unroll
+                    for (int u = 0; u < MU; ++u) {              // in the order of the splits
+                        const float wgt = mv[u] == -INFINITY ? 0.f : expf(mv[u] - nb);
+                        a += av[u] * wgt;
+                        lsum += lv[u] * wgt;
+                    }
+                    big = nb;
                 }
                 out[((size_t)row * nh + head) * D + j] = from_f<bf16>(a / lsum);
             }
@@ -542,6 +617,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 constexpr int kMaxTickets = 65536;
 __device__ int g_decode_tickets[kMaxTickets];
 
+int g_decode_cluster = 1;    // 0: merge through global memory and tickets even where a cluster could (measurements)
 int g_decode_stages = 0;     // 0: chosen from the grid; 2..4 for measurements (rlis_attention_decode_set_stages)
 
 template <int D, int NSTAGE> constexpr size_t decode_mma_smem_bytes() {
@@ -581,6 +657,8 @@ size_t decode_smem_bytes(int nrep, int d) {
 
 // Floats of scratch that `rlis_attention_decode` needs for these sizes (0 when splits == 1).
 extern "C" void rlis_attention_decode_set_stages(int stages) { g_decode_stages = stages; }
+extern "C" void rlis_attention_decode_set_cluster(int on) { g_decode_cluster = on; }
+
 
 extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, int d, int splits) {
     return splits > 1 ? (long long)n_decode * nh * splits * (d + 2) : 0;
@@ -615,12 +693,16 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
                 tickets = ticket_ptr[dev];
             }
         }
-        merged = tickets != nullptr;
-        // Stages of K/V a warp keeps: what shared memory allows for the CTAs to be resident together
-        // (bytes in flight an SM are what the kernel's rate is made of; see the file's head).
+        // 2, 4 or 8 splits (8: the portable cluster size) of a grid of a few waves are merged inside
+        // a cluster; other sizes schedule badly, and large grids lose more to the clusters' placement
+        // than the merge through global memory costs (batch 64: 117 against 110 us)
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long ctas = (long long)grid.x * grid.y * grid.z;
+        const bool cluster = g_decode_cluster && (splits == 2 || splits == 4 || splits == 8) && ctas <= 4ll * sms;
+        merged = tickets != nullptr || cluster;
+        // Stages of K/V a warp keeps: what shared memory allows for the CTAs to be resident together
+        // (bytes in flight an SM are what the kernel's rate is made of; see the file's head).
         int stages = g_decode_stages;
         if (stages == 0) stages = ctas <= sms ? 4 : (ctas <= 2 * sms ? 3 : 2);
         if (d == 128 && stages > 3) stages = 3;               // 4 stages of 128-wide rows do not fit
@@ -632,9 +714,15 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
                                  (int)decode_mma_smem_bytes<DD, NS>());                                \
             attr_done = true;                                                                          \
         }                                                                                              \
-        rlis_launch(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), stream, \
-            (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
-            ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz); \
+        if (cluster)                                                                                   \
+            rlis_launch_cluster(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), \
+                stream, dim3(1, 1, (unsigned)splits),                                                  \
+                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz, 1); \
+        else                                                                                           \
+            rlis_launch(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), stream, \
+                (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
+                ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz, 0); \
     } while (0)
         if (d == 64) {
             if (stages >= 4) LAUNCH_MMA(64, 4);

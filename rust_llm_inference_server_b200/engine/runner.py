@@ -256,8 +256,9 @@ class ModelRunner:
         if not (self.use_graphs and st.all_decode and self.model.graph_safe):
             return None
         W = 0 if st.logit_rows is None else st.logit_rows.shape[0]
-        # the only way the contexts' lengths reach the launch configuration (ops.decode_splits)
-        return (st.n_seqs, W, min(st.max_decode_ctx // ops.DECODE_MIN_KEYS_PER_SPLIT, 32))
+        # the parts say what else of the step reaches a launch configuration (the number of pieces
+        # decode attention cuts the longest context into)
+        return (st.n_seqs, W, self.model.launch_variant(st))
 
     def forward(self, st: StepContext):
         """Launches the model on a prepared step; float32 logits [wanted, vocab] or None.  The

@@ -11,7 +11,7 @@ import torch
 from .. import ops
 from ..config.model_config import read_config_json
 from ..config.registry import lookup_architecture
-from ..parts.base import build_block, build_norm
+from ..parts.base import Part, build_block, build_norm
 from ..parts.spec import ModelSpec
 from ..weights.loader import PlacedSource, check_checkpoint
 from ..weights.safetensors_io import Checkpoint, open_model_dir
@@ -42,10 +42,18 @@ class Model:
         self.embed = None
         self.lm_head = None
         self._plan_caches()
+        # parts whose launch configuration depends on more than the step's shape
+        self._variant_parts = [p for blk in self.blocks for p in blk.parts()
+                               if getattr(type(p), "launch_variant", Part.launch_variant) is not Part.launch_variant]
         # whether a step of this model can be captured in a CUDA graph: every part launches the
         # same kernels on the same device buffers whatever the host-side lists of the step hold
         self.graph_safe = all(getattr(p, "graph_safe", False) for blk in self.blocks for p in blk.parts()) \
             and getattr(self.final_norm, "graph_safe", False)
+
+    def launch_variant(self, step) -> tuple:
+        """What of a decode step, beyond its shape, reaches a launch configuration: steps with the
+        same value can replay the same captured graph."""
+        return tuple(p.launch_variant(step) for p in self._variant_parts)
 
     # ---- what the cache manager has to provide ----
 

@@ -252,6 +252,7 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 NUM_SMS = 148
+DECODE_CLUSTER_MAX_CTAS = 4 * 148     # larger grids merge their pieces through global memory instead
 DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
@@ -259,15 +260,17 @@ def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
     """How many pieces the context is cut into for decode attention (role of `split_plan`,
     crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs): enough CTAs
     (kv heads x requests x splits) to fill the SMs about twice, four pieces for long contexts in
-    any case (it evens out the tail of large batches), each piece at least 128 keys long."""
+    any case (it evens out the tail of large batches), each piece at least 128 keys long.  Up to
+    8 pieces of a small grid are merged inside a thread-block cluster, and clusters of 2, 4 and 8
+    are the sizes that schedule well (batch 8, context 4096: 17.4 us with 4 pieces, 29.2 with 5)."""
     groups = max(1, n_decode * n_kv_heads)
     want = -(-2 * NUM_SMS // groups)
-    # just above two CTAs an SM: one piece fewer keeps them at two an SM, where the kernel has the
-    # shared memory for a third stage of keys in flight (measured: 19.5 against 21.0 us at batch 8)
-    if 2 * NUM_SMS < want * groups <= 2.2 * NUM_SMS and (want - 1) * groups >= 1.6 * NUM_SMS:
-        want -= 1
-    want = max(want, min(4, max_ctx // 512))
-    return max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 32))
+    if groups * 4 > DECODE_CLUSTER_MAX_CTAS:
+        want = max(want, min(4, max_ctx // 512))
+    want = max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 32))
+    if 1 < want < 16 and groups * min(want, 8) <= DECODE_CLUSTER_MAX_CTAS:
+        want = 1 << (min(want, 8).bit_length() - 1)
+    return want
 
 
 def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, block_tables,

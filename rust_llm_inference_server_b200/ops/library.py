@@ -67,6 +67,8 @@ def lib():
         handle.rlis_stream_gemm_set_target.restype = None
         handle.rlis_attention_decode_set_stages.argtypes = [c_int]
         handle.rlis_attention_decode_set_stages.restype = None
+        handle.rlis_attention_decode_set_cluster.argtypes = [c_int]
+        handle.rlis_attention_decode_set_cluster.restype = None
         handle.rlis_set_pdl.argtypes = [c_int]
         handle.rlis_set_pdl.restype = None
         if os.environ.get("RLIS_PDL", "1") == "0":      # programmatic dependent launch is on unless switched off

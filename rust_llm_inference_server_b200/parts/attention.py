@@ -50,6 +50,11 @@ class GQAAttention(Mixer):
         s = self.spec
         return KVCacheSpec(s.n_kv_heads, s.head_dim, s.window)
 
+    def launch_variant(self, step):
+        # decode attention cuts the context into pieces by the longest context of the step
+        s = self.spec
+        return ops.decode_splits(step.n_decode, s.n_kv_heads, step.max_decode_ctx) if step.n_decode else None
+
     def forward(self, x, step, cache, state, writes_cache=True):
         s = self.spec
         T = x.shape[0]

@@ -29,6 +29,12 @@ class Part:
     # lists), so that a decode step can be replayed from a captured CUDA graph.
     graph_safe = False
 
+    def launch_variant(self, step):
+        """For graph-safe parts: whatever of a decode step, beyond the number of requests and of
+        wanted rows, decides a launch configuration (a hashable value; None: nothing does).  Steps
+        with equal variants replay the same captured graph."""
+        return None
+
     def tensors(self) -> dict:
         """Checkpoint tensors this part reads: {name: shape}."""
         return {}
