@@ -217,7 +217,7 @@ struct DecodeQkv {
     bf16* v_cache;
 };
 
-constexpr int DEC_TABLE_SLOTS = 1024;     // block-table entries of a CTA kept in shared memory
+constexpr int DEC_TABLE_SLOTS = 512;      // block-table entries of a CTA kept in shared memory (2 KB: three CTAs of head size 64 still fit an SM)
 
 
 template <int D, int NSTAGE>
