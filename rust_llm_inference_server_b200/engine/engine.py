@@ -124,6 +124,7 @@ class LLMEngine:
         self._fparams_dev = torch.empty((cfg.max_num_seqs, 5), dtype=torch.int32, device=model.device)
         self._fids_dev = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
         self._fids_host = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
+        self._sampled = torch.cuda.Event()      # the sampled ids have arrived in pinned memory
 
     # ---- intake ----
 
@@ -228,7 +229,8 @@ class LLMEngine:
             self.stats.h2d_bytes += n * 20
             launched = True
         if launched:
-            torch.cuda.current_stream().synchronize()
+            self._sampled.record()                  # on the current stream
+            self._sampled.synchronize()
             self.stats.d2h_bytes += n * 4
             a, b = self._ids_host[:n].tolist(), self._fids_host[:n].tolist()
             for i in range(n):

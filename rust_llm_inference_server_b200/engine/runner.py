@@ -61,9 +61,17 @@ class StepContext:
         self.prefill_rows = None                  # int32: rows of the tokens of longer entries
         self.n_prefill_tiles = 0
         self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token), 64 tokens a tile
+        self.n_wanted = 0                         # rows whose logits are asked for
+        self._views = None
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self._runner.workspace(name, shape, dtype)
+
+    def materialize(self) -> None:
+        """Makes the device arrays of the step (see `ModelRunner.prepare`); idempotent."""
+        if self._views is not None:
+            self._views()
+            self._views = None
 
 
 class ModelRunner:
@@ -214,15 +222,7 @@ class ModelRunner:
         self._upload_done.record()
 
         st = StepContext(self, T, B)
-        st.token_ids = dev[o_tok:o_tok + T]
-        st.positions = dev[o_pos:o_pos + T]
-        st.seq_of_token = dev[o_sot:o_sot + T]
-        st.slots = [dev[o_slots + g * Ta:o_slots + g * Ta + T] for g in range(G)]
-        st.block_tables = [dev[o_bt + g * B * mb:o_bt + (g + 1) * B * mb].view(B, mb) for g in range(G)]
-        st.ctx_lens = dev[o_ctx:o_ctx + B]
-        st.cu_seqlens = dev[o_cu:o_cu + B + 1]
-        st.state_slots = dev[o_ss:o_ss + B]
-        st.logit_rows = dev[o_rows:o_rows + W] if W else None
+        st.n_wanted = W
         st.q_lens = lens
         st.starts = starts
         st.state_slot_ids = h[o_ss:o_ss + B].tolist()
@@ -235,16 +235,34 @@ class ModelRunner:
         st.n_decode = Bd
         st.n_prefill_tokens = Tp
         st.n_prefill_tiles = Nt
-        if Nt:
-            st.prefill_tiles = dev[o_pt:o_pt + 2 * Nt].view(Nt, 2)
         if Bd:
-            st.dec_rows = dev[o_dr:o_dr + Bd]
-            st.dec_seqs = dev[o_ds:o_ds + Bd]
             st.max_decode_ctx = max(starts[b] + 1 for b in dec_seqs)
-            st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
+
+        def views():
+            # The step's arrays as views of the uploaded block.  A step replayed from a graph never
+            # looks at them (the graph reads the same addresses), so they are made on demand: a
+            # dozen tensor views cost more host time than the rest of this function.
+            st.token_ids = dev[o_tok:o_tok + T]
+            st.positions = dev[o_pos:o_pos + T]
+            st.seq_of_token = dev[o_sot:o_sot + T]
+            st.slots = [dev[o_slots + g * Ta:o_slots + g * Ta + T] for g in range(G)]
+            st.block_tables = [dev[o_bt + g * B * mb:o_bt + (g + 1) * B * mb].view(B, mb) for g in range(G)]
+            st.ctx_lens = dev[o_ctx:o_ctx + B]
+            st.cu_seqlens = dev[o_cu:o_cu + B + 1]
+            st.state_slots = dev[o_ss:o_ss + B]
+            st.logit_rows = dev[o_rows:o_rows + W] if W else None
+            if Nt:
+                st.prefill_tiles = dev[o_pt:o_pt + 2 * Nt].view(Nt, 2)
+            if Bd:
+                st.dec_rows = dev[o_dr:o_dr + Bd]
+                st.dec_seqs = dev[o_ds:o_ds + Bd]
+                st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
+
+        st._views = views
         return st
 
     def _forward_eager(self, st: StepContext):
+        st.materialize()
         resid, delta = self.model.forward(st, self._caches, self._states)
         if st.logit_rows is None:
             return None
@@ -255,7 +273,7 @@ class ModelRunner:
         graph: the launch-bound inner loop of generation (about ten kernels a layer)."""
         if not (self.use_graphs and st.all_decode and self.model.graph_safe):
             return None
-        W = 0 if st.logit_rows is None else st.logit_rows.shape[0]
+        W = st.n_wanted
         # the parts say what else of the step reaches a launch configuration (the number of pieces
         # decode attention cuts the longest context into)
         return (st.n_seqs, W, self.model.launch_variant(st))

@@ -10,6 +10,8 @@ no reduced-precision matrix mode can enter.
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from .library import KernelError, check, lib
@@ -35,7 +37,14 @@ def _code(dtype) -> int:
         raise KernelError(f"element type {dtype} is not supported (float32 and bfloat16 are)") from None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  (The raw lookup takes a microsecond; building a
+    `torch.cuda.Stream` object for it took eighteen, three times a decode step.)"""
+    if _raw_stream is not None:
+        return _raw_stream(-1)
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -256,6 +265,7 @@ DECODE_CLUSTER_MAX_CTAS = 4 * 148     # larger grids merge their pieces through 
 DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
+@functools.lru_cache(maxsize=4096)
 def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
     """How many pieces the context is cut into for decode attention (role of `split_plan`,
     crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs): enough CTAs
