@@ -20,6 +20,7 @@ class EngineConfig:
     max_seq_len: int = 2048           # longest prompt plus completion
     num_blocks: int | None = None     # if given, overrides kv_cache_bytes (pages per group)
     cuda_graphs: bool = True          # replay decode-only steps from captured graphs
+    decode_ahead: bool = True         # launch the next decode step before this one's tokens reach the host
 
     def validate(self) -> None:
         if self.policy not in ("continuous", "static"):

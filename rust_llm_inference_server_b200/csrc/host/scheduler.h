@@ -99,6 +99,15 @@ public:
         if (SeqState* s = find_running(id)) s->tokens.push_back(token);
     }
 
+    // Replaces the token at `index` (a placeholder that was appended for a step launched before
+    // the token was known).  The sequence may have been preempted in the meantime.
+    void set_token(SeqId id, size_t index, int32_t token) {
+        SeqState* s = find_any_mutable(id);
+        if (!s) return;
+        if (index >= s->tokens.size()) throw std::out_of_range("set_token: no such token");
+        s->tokens[index] = token;
+    }
+
     bool is_caught_up(SeqId id) const {
         for (auto& s : running_)
             if (s.id == id) return s.num_computed == s.tokens.size();
@@ -161,6 +170,10 @@ private:
         for (auto& s : waiting_) if (s.id == id) return &s;
         for (auto& s : preempted_) if (s.id == id) return &s;
         return nullptr;
+    }
+
+    SeqState* find_any_mutable(SeqId id) {
+        return const_cast<SeqState*>(static_cast<const Scheduler*>(this)->find_any(id));
     }
 
     SeqState* find_running(SeqId id) {

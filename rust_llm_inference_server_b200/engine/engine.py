@@ -3,6 +3,15 @@ samples, finishes and frees.
 
 Role of `Engine::{iterate, step}` and `Sequence::accept` (crates/engine/src/engine.rs:500-531,
 617-726, 404-429) without the thread, channels and text side: token ids in, token ids out.
+
+Decode-ahead.  While every running request decodes, the next step needs nothing from the host but
+the tokens just sampled, and those are on the device already.  The engine then launches step k + 1
+(its token ids copied on the device from step k's sampler output) before it waits for step k's
+ids, so the host's work on step k (reading the ids, end-of-sequence checks, scheduling, packing
+the next step) runs while the GPU computes.  A request that ends on an end-of-sequence token has
+by then one more step in flight; that step's row is dropped when it arrives.  Tokens and their
+order are those of the step-by-step loop (the reference's loop is step by step,
+engine.rs:617-726).
 """
 
 from __future__ import annotations
@@ -52,6 +61,23 @@ class _Sequence:
     arrived: float
     first_token_at: float | None = None
     finished: bool = False
+
+
+@dataclass
+class _Launched:
+    """A step that has been launched; its sampled ids may still be on their way to the host."""
+    seqs: list                    # (request id, start, end) as scheduled
+    rows: list                    # the _Sequence of each wanted row (requests whose tokens are all computed)
+    n_tokens: int
+    n_seqs: int
+    all_decode: bool
+    logits: object = None
+    slot: int = 0                 # which pinned buffers and event hold its ids
+    plain: list = field(default_factory=list)      # per row: parameters of the Gumbel-max kernel or None
+    filt: list = field(default_factory=list)       # per row: parameters of the filtering kernel or None
+    pos: list = field(default_factory=list)        # per row: index of the token being sampled
+    ahead: bool = False           # launched before its input tokens were known to the host
+    ids_dev: object = None        # device ids of all rows, when one kernel sampled them all
 
 
 @dataclass
@@ -116,15 +142,23 @@ class LLMEngine:
         self.seqs: dict[int, _Sequence] = {}
         self._next_id = 0
         self.stats = EngineStats()
-        self._params_host = torch.empty((cfg.max_num_seqs, 2), dtype=torch.int32, pin_memory=True)
-        self._params_dev = torch.empty((cfg.max_num_seqs, 2), dtype=torch.int32, device=model.device)
-        self._ids_dev = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
-        self._ids_host = torch.empty((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
-        self._fparams_host = torch.empty((cfg.max_num_seqs, 5), dtype=torch.int32, pin_memory=True)
-        self._fparams_dev = torch.empty((cfg.max_num_seqs, 5), dtype=torch.int32, device=model.device)
-        self._fids_dev = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, device=model.device)
-        self._fids_host = torch.zeros((cfg.max_num_seqs,), dtype=torch.int32, pin_memory=True)
-        self._sampled = torch.cuda.Event()      # the sampled ids have arrived in pinned memory
+        # Two steps can be in flight (decode-ahead), so what the host writes or reads per step
+        # exists twice: pinned parameter and id buffers and the event that says the ids arrived.
+        # The device-side buffers are used in stream order and exist once.
+        n = cfg.max_num_seqs
+        pinned = lambda shape: [torch.zeros(shape, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._params_host, self._fparams_host = pinned((n, 2)), pinned((n, 5))
+        self._ids_host, self._fids_host = pinned((n,)), pinned((n,))
+        self._params_dev = torch.empty((n, 2), dtype=torch.int32, device=model.device)
+        self._fparams_dev = torch.empty((n, 5), dtype=torch.int32, device=model.device)
+        self._ids_dev = torch.zeros((n,), dtype=torch.int32, device=model.device)
+        self._fids_dev = torch.zeros((n,), dtype=torch.int32, device=model.device)
+        self._sampled = [torch.cuda.Event(), torch.cuda.Event()]
+        self._slot = 0
+        self._inflight: _Launched | None = None
+        # pages of a window group are handed out as a request grows, so a decode step can run out
+        # of pages and preempt: such models are stepped one by one
+        self._decode_ahead = bool(cfg.decode_ahead) and all(not g.window for g in groups)
 
     # ---- intake ----
 
@@ -153,104 +187,166 @@ class LLMEngine:
             self.sched.remove(request_id)
 
     def has_work(self) -> bool:
-        return self.sched.has_work()
+        return self.sched.has_work() or self._inflight is not None
 
     # ---- one iteration ----
 
     def step(self) -> list:
-        """Schedules, runs and samples one step; returns the requests that finished in it."""
+        """One turn of the loop: makes sure a step is in flight, launches the one after it where
+        that is possible (see the module's head), then reads the first one's tokens.  Returns the
+        requests that finished with them."""
+        cur, self._inflight = self._inflight, None
+        if cur is None:
+            cur = self._launch(None)
+            if cur is None:
+                self.last_step = StepEvent(0, 0, False, {}, [])
+                return []
+        nxt = self._launch(cur) if self._may_run_ahead(cur) else None
+        new_tokens, finished = self._collect(cur, nxt)
+        self._inflight = nxt
+        self._publish()
+        self.last_step = StepEvent(cur.n_tokens, cur.n_seqs, cur.all_decode, new_tokens, finished)
+        return finished
+
+    def _may_run_ahead(self, cur: _Launched) -> bool:
+        """The step after `cur` can be launched before `cur`'s tokens are known: every request of
+        `cur` gets a token from the device (one kernel for all), goes on after it whatever it is,
+        unless it is an end-of-sequence token, and nobody waits to be admitted."""
+        if not self._decode_ahead or not cur.rows or len(cur.rows) != len(cur.seqs) or cur.ids_dev is None:
+            return False
+        if self.sched.num_waiting() != 0:
+            return False
+        for s in cur.rows:
+            if s.id not in self.seqs or len(s.tokens) + 1 - s.prompt_len >= s.max_tokens:
+                return False
+        return True
+
+    def _launch(self, prev: _Launched | None) -> _Launched | None:
+        """Schedules and launches a step and its sampler; waits for nothing.  With `prev`, the step
+        is the one after `prev`, whose tokens are still on the device: every request gets a
+        placeholder, and the token ids are copied on the device from `prev`'s sampler output."""
+        if prev is not None:
+            for s in prev.rows:
+                self.sched.append_token(s.id, 0)
         seqs, preempted = self.sched.schedule()
         self.stats.preemptions += len(preempted)
+        if prev is not None:
+            want = [(s.id, len(s.tokens), len(s.tokens) + 1) for s in prev.rows]
+            if preempted or [tuple(x) for x in seqs] != want:
+                raise RuntimeError("decode-ahead: the scheduler did not continue the running requests as they were")
         if not seqs:
-            self.last_step = StepEvent(0, 0, False, {}, [])
             if self.sched.has_work():
                 # no progress is possible: fail everything rather than spin (engine.rs:516-522)
                 ids = list(self.seqs)
                 for sid in ids:
                     self.cancel(sid)
                 raise RuntimeError(f"scheduler made no progress with {len(ids)} requests pending")
-            return []
+            return None
         entries = []
-        sample_rows = []            # (sequence, row among the wanted rows)
+        rows = []
         for sid, start, end in seqs:
             s = self.seqs[sid]
+            if prev is not None:
+                entries.append(StepEntry(sid, [0], start, [0]))
+                rows.append(s)
+                continue
             caught_up = end == len(s.tokens)
             entries.append(StepEntry(sid, s.tokens[start:end], start, [end - start - 1] if caught_up else []))
             if caught_up:
-                sample_rows.append(s)
+                rows.append(s)
         st = self.runner.prepare(entries)
+        if prev is not None:
+            st.take_tokens(prev.ids_dev[:len(rows)])
         logits = self.runner.forward(st)
         self.stats.h2d_bytes += st.h2d_bytes
         self.stats.steps += 1
         self.stats.step_tokens += st.n_tokens
-        for sid, start, end in seqs:
-            self.sched.advance(sid, end)
-        finished = []
-        new_tokens = {}
-        if sample_rows:
-            tokens = self._sample(logits, sample_rows)
-            now = time.perf_counter()
-            for s, tok in zip(sample_rows, tokens):
-                new_tokens[s.id] = int(tok)
-                out = self._accept(s, int(tok), now)
-                if out is not None:
-                    finished.append(out)
-        self._publish()
-        self.last_step = StepEvent(st.n_tokens, st.n_seqs, st.all_decode, new_tokens, finished)
-        return finished
-
-    def _sample(self, logits: torch.Tensor, rows: list) -> list:
-        """One token per caught-up request.  Greedy and temperature rows: the device's Gumbel-max
-        kernel; top-k / top-p rows: the device's filtering kernel; rows with a repetition penalty:
-        the host (crates/engine/src/engine.rs:643-708 has the same split, with all filtering on
-        the host).  Only token ids come back, except for host rows."""
-        n = len(rows)
-        pos = [len(s.tokens) for s in rows]
-        plain = [s.sampler.device_mode(p) for s, p in zip(rows, pos)]
-        filt = [s.sampler.filtered_mode(p) if m is None else None for s, p, m in zip(rows, pos, plain)]
-        out = [0] * n
-        launched = False
-        if any(m is not None for m in plain):
-            ph = self._params_host.numpy().view(np.uint32)
-            for i in range(n):
-                ph[i] = plain[i] if plain[i] is not None else (0, 0)
-            self._params_dev[:n].copy_(self._params_host[:n], non_blocking=True)
-            ops.sample_rows(logits, self._params_dev[:n], self._ids_dev[:n])
-            self._ids_host[:n].copy_(self._ids_dev[:n], non_blocking=True)
-            self.stats.h2d_bytes += n * 8
-            launched = True
-        if any(f is not None for f in filt):
-            fh = self._fparams_host.numpy().view(np.uint32)
-            for i in range(n):
-                fh[i] = filt[i] if filt[i] is not None else (float_bits(1.0), 1, float_bits(1.0), 0, 0)
-            self._fparams_dev[:n].copy_(self._fparams_host[:n], non_blocking=True)
-            ops.sample_filtered(logits, self._fparams_dev[:n], self._fids_dev[:n])
-            self._fids_host[:n].copy_(self._fids_dev[:n], non_blocking=True)
-            self.stats.h2d_bytes += n * 20
-            launched = True
-        if launched:
-            self._sampled.record()                  # on the current stream
-            self._sampled.synchronize()
-            self.stats.d2h_bytes += n * 4
-            a, b = self._ids_host[:n].tolist(), self._fids_host[:n].tolist()
-            for i in range(n):
-                if plain[i] is not None:
-                    out[i] = a[i]
-                elif filt[i] is not None:
-                    out[i] = b[i]
-        host_idx = [i for i in range(n) if plain[i] is None and filt[i] is None]
-        if host_idx:
-            sel = torch.tensor(host_idx, device=logits.device)
-            rows_host = logits.index_select(0, sel).to("cpu").numpy()
-            self.stats.d2h_bytes += rows_host.nbytes
-            for j, i in enumerate(host_idx):
-                s = rows[i]
-                out[i] = s.sampler.sample_host(rows_host[j], s.tokens, pos[i])
+        self._slot ^= 1
+        out = _Launched(list(seqs), rows, st.n_tokens, st.n_seqs, st.all_decode, logits, self._slot,
+                        ahead=prev is not None)
+        if prev is None:
+            # (for a step launched ahead this waits until its input tokens are real: `_collect`)
+            for sid, start, end in seqs:
+                self.sched.advance(sid, end)
+        if rows:
+            self._enqueue_sampler(out)
         return out
 
-    def _accept(self, s: _Sequence, token: int, now: float):
+    def _enqueue_sampler(self, L: _Launched) -> None:
+        """Launches the samplers of a step's wanted rows and the copy of their ids to pinned
+        memory.  Greedy and temperature rows: the device's Gumbel-max kernel; top-k / top-p rows:
+        the device's filtering kernel; rows with a repetition penalty: the host, when the ids are
+        read (crates/engine/src/engine.rs:643-708 has the same split, with all filtering on the
+        host)."""
+        rows, n, k = L.rows, len(L.rows), L.slot
+        L.pos = [len(s.tokens) + (1 if L.ahead else 0) for s in rows]
+        L.plain = [s.sampler.device_mode(p) for s, p in zip(rows, L.pos)]
+        L.filt = [s.sampler.filtered_mode(p) if m is None else None for s, p, m in zip(rows, L.pos, L.plain)]
+        n_plain = sum(m is not None for m in L.plain)
+        n_filt = sum(f is not None for f in L.filt)
+        if n_plain:
+            ph = self._params_host[k].numpy().view(np.uint32)
+            for i in range(n):
+                ph[i] = L.plain[i] if L.plain[i] is not None else (0, 0)
+            self._params_dev[:n].copy_(self._params_host[k][:n], non_blocking=True)
+            ops.sample_rows(L.logits, self._params_dev[:n], self._ids_dev[:n])
+            self._ids_host[k][:n].copy_(self._ids_dev[:n], non_blocking=True)
+            self.stats.h2d_bytes += n * 8
+        if n_filt:
+            fh = self._fparams_host[k].numpy().view(np.uint32)
+            for i in range(n):
+                fh[i] = L.filt[i] if L.filt[i] is not None else (float_bits(1.0), 1, float_bits(1.0), 0, 0)
+            self._fparams_dev[:n].copy_(self._fparams_host[k][:n], non_blocking=True)
+            ops.sample_filtered(L.logits, self._fparams_dev[:n], self._fids_dev[:n])
+            self._fids_host[k][:n].copy_(self._fids_dev[:n], non_blocking=True)
+            self.stats.h2d_bytes += n * 20
+        if n_plain or n_filt:
+            self._sampled[k].record()               # on the current stream
+            self.stats.d2h_bytes += n * 4
+        if n_plain == n:
+            L.ids_dev = self._ids_dev
+        elif n_filt == n:
+            L.ids_dev = self._fids_dev
+
+    def _collect(self, L: _Launched, nxt: _Launched | None):
+        """Waits for a launched step's ids, records the tokens and finishes requests.  `nxt`: the
+        step launched after it with placeholders, which now get their values."""
+        new_tokens, finished = {}, []
+        rows, n, k = L.rows, len(L.rows), L.slot
+        if rows:
+            tokens = [0] * n
+            if any(m is not None for m in L.plain) or any(f is not None for f in L.filt):
+                self._sampled[k].synchronize()
+                a, b = self._ids_host[k][:n].tolist(), self._fids_host[k][:n].tolist()
+                for i in range(n):
+                    tokens[i] = a[i] if L.plain[i] is not None else b[i]
+            host_idx = [i for i in range(n) if L.plain[i] is None and L.filt[i] is None]
+            if host_idx:
+                sel = torch.tensor(host_idx, device=L.logits.device)
+                rows_host = L.logits.index_select(0, sel).to("cpu").numpy()
+                self.stats.d2h_bytes += rows_host.nbytes
+                for j, i in enumerate(host_idx):
+                    s = rows[i]
+                    tokens[i] = s.sampler.sample_host(rows_host[j], s.tokens, L.pos[i])
+            now = time.perf_counter()
+            for s, tok in zip(rows, tokens):
+                if s.id not in self.seqs:           # cancelled, or ended one step earlier (its row ran ahead)
+                    continue
+                new_tokens[s.id] = int(tok)
+                out = self._accept(s, int(tok), now, placeholder=nxt is not None)
+                if out is not None:
+                    finished.append(out)
+        if nxt is not None:
+            # its input tokens are real now: pages they fill may enter the prefix registry
+            for sid, start, end in nxt.seqs:
+                if sid in self.seqs:
+                    self.sched.advance(sid, end)
+        return new_tokens, finished
+
+    def _accept(self, s: _Sequence, token: int, now: float, placeholder: bool = False):
         """Records a sampled token; finishes the request on end-of-sequence (not appended) unless
-        `ignore_eos`, or at `max_tokens` (engine.rs:404-429)."""
+        `ignore_eos`, or at `max_tokens` (engine.rs:404-429).  `placeholder`: the scheduler holds
+        a placeholder for this token already (the next step has been launched)."""
         if s.first_token_at is None:
             s.first_token_at = now
         if token in self.eos_ids and not s.ignore_eos:
@@ -259,7 +355,10 @@ class LLMEngine:
         self.stats.generated_tokens += 1
         if len(s.tokens) - s.prompt_len >= s.max_tokens:
             return self._finish(s, "length", now)
-        self.sched.append_token(s.id, token)
+        if placeholder:
+            self.sched.set_token(s.id, len(s.tokens) - 1, token)
+        else:
+            self.sched.append_token(s.id, token)
         return None
 
     def _finish(self, s: _Sequence, reason: str, now: float) -> RequestOutput:

@@ -24,14 +24,15 @@ class LLM:
                  kv_cache_gb: float = 1.0, block_size: int = 16, max_num_seqs: int = 64,
                  max_batched_tokens: int = 2048, scheduler: str = "continuous",
                  prefix_caching: bool = True, num_blocks: int | None = None, device: str = "cuda",
-                 cuda_graphs: bool = True, _model=None):
+                 cuda_graphs: bool = True, decode_ahead: bool = True, _model=None):
         if not torch.cuda.is_available():
             raise RuntimeError("this engine runs on a CUDA device only; there is no CPU path")
         self.model = _model if _model is not None else load_model(model, dtype, device)
         cfg = EngineConfig(max_num_seqs=max_num_seqs, max_batched_tokens=max_batched_tokens,
                            kv_cache_bytes=int(kv_cache_gb * (1 << 30)), block_size=block_size,
                            policy=scheduler, prefix_caching=prefix_caching, max_seq_len=max_seq_len,
-                           num_blocks=num_blocks, cuda_graphs=cuda_graphs)
+                           num_blocks=num_blocks, cuda_graphs=cuda_graphs,
+                           decode_ahead=decode_ahead)
         self.engine = LLMEngine(self.model, cfg)
 
     @classmethod

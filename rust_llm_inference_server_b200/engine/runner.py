@@ -63,9 +63,15 @@ class StepContext:
         self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token), 64 tokens a tile
         self.n_wanted = 0                         # rows whose logits are asked for
         self._views = None
+        self._token_region = None
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self._runner.workspace(name, shape, dtype)
+
+    def take_tokens(self, ids: torch.Tensor) -> None:
+        """Replaces the step's token ids by `ids` (int32 on the device, one per token), in stream
+        order: after the upload of the step's arrays, before its kernels."""
+        self._token_region().copy_(ids)
 
     def materialize(self) -> None:
         """Makes the device arrays of the step (see `ModelRunner.prepare`); idempotent."""
@@ -259,6 +265,7 @@ class ModelRunner:
                 st.prefill_rows = dev[o_pr:o_pr + Tp] if Tp else None
 
         st._views = views
+        st._token_region = lambda: dev[o_tok:o_tok + T]
         return st
 
     def _forward_eager(self, st: StepContext):

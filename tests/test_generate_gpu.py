@@ -166,3 +166,56 @@ def test_end_of_sequence_and_limits(model_root, tmp_path):
     with pytest.raises(RequestError, match="vocabulary"):
         llm.generate([[1, 999]], SamplingParams())
     assert llm.engine.cache.num_free_pages(0) == 16
+
+
+def test_decode_ahead_changes_no_token(model_root, tmp_path):
+    """The loop that launches a step before the one before it has been read gives the tokens,
+    finish reasons and order of events of the step-by-step loop: greedy and seeded sampling,
+    requests of different lengths (so that the batch shrinks), an end-of-sequence token that
+    arrives while the next step is already in flight, a cancelled request, and requests that
+    arrive while others decode."""
+    import json, os, shutil
+    from rust_llm_inference_server_b200 import LLM, SamplingParams
+    src = make_model_dir(model_root, "B")
+    w = load_plain_weights(src)
+    prompts = prompts_for("B", [5, 19, 9, 33], seed=4)
+    # an end-of-sequence token that the first request meets after a few tokens
+    greedy = P.greedy_generate(w, CONFIGS["B"], prompts[0], 12)
+    eos = next(t for i, t in enumerate(greedy) if i >= 3 and t not in greedy[:i])     # first met after a few tokens
+    d = str(tmp_path / "with_eos")
+    shutil.copytree(src, d)
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    cfg["eos_token_id"] = int(eos)
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    opts = dict(dtype="float32", max_seq_len=128, num_blocks=64, block_size=8, max_num_seqs=4)
+    runs = {}
+    for ahead in (False, True):
+        llm = LLM(d, decode_ahead=ahead, **opts)
+        sps = [SamplingParams(max_tokens=20), SamplingParams(max_tokens=7, ignore_eos=True),
+               SamplingParams(max_tokens=25, temperature=0.8, seed=5, ignore_eos=True),
+               SamplingParams(max_tokens=16, temperature=1.0, top_k=9, top_p=0.9, seed=6, ignore_eos=True)]
+        outs = llm.generate(prompts, sps)
+        runs[ahead] = [(o.token_ids, o.finish_reason) for o in outs]
+        # the stream of events: a request joins while the others decode, another is cancelled
+        eng = llm.engine
+        a = eng.add_request(prompts[1], SamplingParams(max_tokens=12, ignore_eos=True))
+        b = eng.add_request(prompts[2], SamplingParams(max_tokens=30, ignore_eos=True))
+        seen, done, step = {a: [], b: []}, {}, 0
+        c = None
+        while eng.has_work():
+            for o in eng.step():
+                done[o.request_id] = (o.token_ids, o.finish_reason)
+            for rid, t in eng.last_step.new_tokens.items():
+                seen.setdefault(rid, []).append(t)
+            step += 1
+            if step == 4:
+                c = eng.add_request(prompts[3], SamplingParams(max_tokens=6, ignore_eos=True))
+            if step == 9:
+                eng.cancel(b)
+        assert b not in done and done[a][0] == seen[a] and done[c][0] == seen[c] and len(seen[c]) == 6
+        runs[ahead].append((done[a], done[c], seen[b][:8]))
+        assert eng.sched.check() == "" and eng.sched.num_running() == 0
+        if ahead:
+            assert llm.engine._decode_ahead
+    assert runs[True] == runs[False]
+    assert runs[True][0] == (greedy[:greedy.index(eos)], "stop")           # ended by the end-of-sequence token
