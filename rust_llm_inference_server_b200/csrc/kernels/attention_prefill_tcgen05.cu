@@ -1,0 +1,401 @@
+// Causal flash attention for portions of prompts over the paged cache on the fifth-generation
+// tensor cores (bfloat16, head size 64, an even number of query heads per kv head, page sizes
+// 8 .. 128 that divide 128).  Same contract as attention_prefill.cu (role in the reference: the
+// fused `sdpa` call for multi-token segments, crates/model/src/attention.rs:144-157; scores in
+// float32, keys after the query hidden, softmax in float32, attention.rs:204-233), which stays
+// for the other sizes.
+//
+// One CTA = 64 tokens of one request x TWO query heads of one kv head: the 128 rows of the tensor
+// instruction are (head 0, tokens 0..63), (head 1, tokens 0..63), so every key and value tile is
+// used by both heads.  Per block of 128 keys:
+//   warp 0, one lane: TMA.  Q once (two 64 x 64 boxes); the block's K and V page by page (a page
+//           of one kv head is a [page_size x 64] box of the cache seen as a 2-D tensor; pages
+//           past the context are asked for past the end of the tensor and arrive as zeros) into
+//           a ring of two stages, 128-byte swizzle.
+//   warp 1, one lane: S = Q K^T (tcgen05.mma, M 128, N 128, K 64) into tensor memory; after the
+//           softmax warps have written P: O_j = P V (M 128, N 64, K 128; V is the MN-major
+//           operand, straight from the cache's layout), a fresh accumulator per block.
+//   warps 2-5: a thread per row.  Two passes over its row of S in tensor memory (maximum, then
+//           exp2 and sum), P rounded to bf16 into shared memory in the swizzled K-major layout
+//           the tensor core reads; then o = o * correction + O_j in registers.
+// Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
+// other's gaps between the phases.
+//
+// Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets the error word
+// (rlis_attention_prefill_tc_error), every role runs to its end without further waits, and the
+// CTA frees its tensor memory before it returns.
+#include "tcgen05_utils.cuh"
+#include <math.h>
+
+namespace {
+using namespace tc;
+constexpr int TQ = 64;                  // tokens of a CTA
+constexpr int TM = 128;                 // rows of the instruction: two heads x 64 tokens
+constexpr int TN = 128;                 // keys of a block
+constexpr int HD = 64;                  // head size
+constexpr int KV_STAGES = 2;
+constexpr int Q_BYTES = TM * HD * 2;            // 16 KB
+constexpr int KV_TILE_BYTES = TN * HD * 2;      // 16 KB each for K and V
+constexpr int P_BYTES = TM * TN * 2;            // 32 KB: two [128 x 64] swizzled halves
+constexpr int PT_THREADS = 192;
+// 112 KB of tiles + the control block; with the kilobyte the system keeps per CTA, two CTAs fit the
+// 228 KB of an SM only if no alignment slack is spent: the dynamic array is declared 1024-aligned
+constexpr size_t PT_SMEM = Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES + 128;
+constexpr uint32_t TMEM_COLS = 256;             // S: columns 0..127, O_j: 128..191
+constexpr uint32_t IDESC_S = idesc_bf16(TM, TN);
+constexpr uint32_t IDESC_PV = idesc_bf16(TM, HD) | (1u << 16);      // B (V) is MN-major
+
+struct PCtrl {
+    uint64_t q_full;
+    uint64_t kv_full[KV_STAGES];
+    uint64_t kv_empty[KV_STAGES];
+    uint64_t s_full, s_empty, p_full, o_full;
+    uint32_t tmem_base;
+    int abort;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Both passes over a row of scores read tensor memory 32 columns at a time, and ask for the next 32
+// before they work on the ones they have: a load from tensor memory takes hundreds of cycles.
+
+template <bool MASK>
+__device__ __forceinline__ void max_of_chunk(const uint32_t (&v)[32], int c, int kmin, int kmax, float& mx) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int idx = c * 32 + i;
+        const float sv = __uint_as_float(v[i]);
+        mx = fmaxf(mx, (!MASK || (idx <= kmax && idx >= kmin)) ? sv : -INFINITY);
+    }
+}
+
+// Pass 1: the row's maximum over the visible keys.
+template <bool MASK>
+__device__ __forceinline__ void softmax_max(uint32_t taddr, int kmin, int kmax, float& mx) {
+    uint32_t va[32], vb[32];
+    tmem_ld32_nowait(taddr, va);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 32u, vb);
+    max_of_chunk<MASK>(va, 0, kmin, kmax, mx);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 64u, va);
+    max_of_chunk<MASK>(vb, 1, kmin, kmax, mx);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 96u, vb);
+    max_of_chunk<MASK>(va, 2, kmin, kmax, mx);
+    tmem_ld_wait();
+    max_of_chunk<MASK>(vb, 3, kmin, kmax, mx);
+}
+
+// P = exp2(s * scale - m) of 32 keys, rounded to bf16 into the row's line of the swizzled tile (two
+// halves of 64 keys; the 16-byte chunk index is XORed with the row's index in its group of 8).
+template <bool MASK>
+__device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int kmin, int kmax, float scale_log2,
+                                             float m_use, unsigned char* prow, int r, float& lsum) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int idx = c * 32 + 2 * i;
+        float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), scale_log2, -m_use));
+        float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, -m_use));
+        if (MASK) {
+            if (!(idx <= kmax && idx >= kmin)) p0 = 0.f;
+            if (!(idx + 1 <= kmax && idx + 1 >= kmin)) p1 = 0.f;
+        }
+        lsum += p0 + p1;
+        pk[i] = pack_bf16(p0, p1);
+    }
+    unsigned char* half = prow + (size_t)(c / 2) * (P_BYTES / 2);
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+        const int chunk = (c % 2) * 4 + ch;
+        *reinterpret_cast<uint4*>(half + (((chunk ^ (r & 7)) & 7) << 4)) =
+            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+    }
+}
+
+// Pass 2: P and the row's sum.
+template <bool MASK>
+__device__ __forceinline__ void softmax_exp(uint32_t taddr, int kmin, int kmax, float scale_log2, float m_use,
+                                            unsigned char* prow, int r, float& lsum) {
+    uint32_t va[32], vb[32];
+    tmem_ld32_nowait(taddr, va);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 32u, vb);
+    exp_of_chunk<MASK>(va, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 64u, va);
+    exp_of_chunk<MASK>(vb, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+    tmem_ld_wait();
+    tmem_ld32_nowait(taddr + 96u, vb);
+    exp_of_chunk<MASK>(va, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+    tmem_ld_wait();
+    exp_of_chunk<MASK>(vb, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+}
+
+__global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
+    const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
+    int cache_rows, float scale, int window) {
+    extern __shared__ __align__(1024) unsigned char pt_smem_raw[];
+    if ((smem_u32(pt_smem_raw) & 1023u) != 0u) {       // the swizzled tiles need it; never seen, but checked
+        if (threadIdx.x == 0) atomicExch(&g_tc_error, 2);
+        return;
+    }
+    unsigned char* q_tile = pt_smem_raw;
+    unsigned char* kv_tiles = q_tile + Q_BYTES;                       // [stage][K|V]
+    unsigned char* p_tile = kv_tiles + KV_STAGES * 2 * KV_TILE_BYTES;
+    PCtrl* ctrl = reinterpret_cast<PCtrl*>(p_tile + P_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nrep = nh / nkv;
+    const int b = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
+    const int head0 = blockIdx.y * 2;
+    const int kvh = head0 / nrep;
+    const int q_start = cu_seqlens[b];
+    const int q_len = cu_seqlens[b + 1] - q_start;
+    const int ctx = ctx_lens[b];
+    const int pos0 = ctx - q_len + t0;                       // position of the tile's first token
+    const int n_valid = min(TQ, q_len - t0);
+    const int* table = block_tables + (size_t)b * max_blocks;
+    const int last_pos = pos0 + n_valid - 1;
+    const int blk_lo = window > 0 ? max(0, pos0 - window + 1) / TN : 0;
+    const int blk_hi = last_pos / TN;                        // inclusive
+    const int n_blk = blk_hi - blk_lo + 1;
+
+    if (threadIdx.x == 0) {
+        ctrl->abort = 0;
+        bar_init(&ctrl->q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            bar_init(&ctrl->kv_full[s], 1);
+            bar_init(&ctrl->kv_empty[s], 1);
+        }
+        bar_init(&ctrl->s_full, 1);
+        bar_init(&ctrl->s_empty, 4);
+        bar_init(&ctrl->p_full, 4);
+        bar_init(&ctrl->o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u;
+    pdl_wait();             // q and this portion's keys come from the kernels before
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bar_expect_tx(&ctrl->q_full, Q_BYTES);
+            tma_load_2d(q_tile, &map_q, head0 * HD, q_start + t0, &ctrl->q_full);
+            tma_load_2d(q_tile + Q_BYTES / 2, &map_q, (head0 + 1) * HD, q_start + t0, &ctrl->q_full);
+            const int pages_per_blk = TN / page_size;
+            const int page_bytes = page_size * HD * 2;
+            for (int it = 0; it < n_blk; ++it) {
+                const int s = it % KV_STAGES;
+                if (it >= KV_STAGES && !bar_wait(&ctrl->kv_empty[s], ((it / KV_STAGES) - 1) & 1, &ctrl->abort)) break;
+                unsigned char* kt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES;
+                unsigned char* vt = kt + KV_TILE_BYTES;
+                bar_expect_tx(&ctrl->kv_full[s], 2 * KV_TILE_BYTES);
+                const int key0 = (blk_lo + it) * TN;
+                for (int p = 0; p < pages_per_blk; ++p) {
+                    const int key = key0 + p * page_size;
+                    // a page past the context, or wholly behind the window of the tile's first token
+                    // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
+                    const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
+                    const int row = wanted ? (table[key / page_size] * nkv + kvh) * page_size : cache_rows;
+                    tma_load_2d(kt + (size_t)p * page_bytes, &map_k, 0, row, &ctrl->kv_full[s]);
+                    tma_load_2d(vt + (size_t)p * page_bytes, &map_v, 0, row, &ctrl->kv_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = bar_wait(&ctrl->q_full, 0, &ctrl->abort);
+            const uint64_t qdesc = smem_desc_sw128(q_tile);
+            auto issue_s = [&](int it) {
+                const int s = it % KV_STAGES;
+                if (!bar_wait(&ctrl->kv_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) return false;
+                // the softmax warps have taken the scores of the block before out of tensor memory
+                if (it > 0 && !bar_wait(&ctrl->s_empty, (it - 1) & 1, &ctrl->abort)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t kdesc = smem_desc_sw128(kv_tiles + (size_t)s * 2 * KV_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k)
+                    umma_bf16(tmem_s, qdesc + (uint64_t)(k * 32 >> 4), kdesc + (uint64_t)(k * 32 >> 4), IDESC_S, k != 0 ? 1u : 0u);
+                umma_commit(&ctrl->s_full);
+                return true;
+            };
+            if (ok && n_blk > 0) ok = issue_s(0);
+            for (int it = 0; it < n_blk && ok; ++it) {
+                const int s = it % KV_STAGES;
+                if (it + 1 < n_blk && !issue_s(it + 1)) break;         // the next block's scores, behind this block's softmax
+                if (!bar_wait(&ctrl->p_full, it & 1, &ctrl->abort)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned char* vt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < TN / 16; ++k) {
+                    // P: two swizzled halves of 64 keys, 32 bytes a step inside a half; V: 16 keys = 2 KB further
+                    const uint64_t pdesc = smem_desc_sw128(p_tile + (size_t)(k / 4) * (P_BYTES / 2)) + (uint64_t)((k % 4) * 32 >> 4);
+                    const uint64_t vdesc = smem_desc_sw128(vt + (size_t)k * 16 * HD * 2);
+                    umma_bf16(tmem_o, pdesc, vdesc, IDESC_PV, k != 0 ? 1u : 0u);
+                }
+                umma_commit(&ctrl->o_full);
+                umma_commit(&ctrl->kv_empty[s]);
+            }
+        }
+    } else {
+        // softmax and output: warp w reads TMEM lanes 32 (w % 4) .. + 31; a lane is a row
+        const int q4 = warp & 3;
+        const int r = q4 * 32 + lane;
+        const int hsel = r >> 6, qi = r & 63;
+        const int pos = pos0 + qi;
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const bool row_valid = qi < n_valid;
+        const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        float m_run = -INFINITY, l_run = 0.f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        unsigned char* prow = p_tile + (size_t)r * 128;          // this row's 128-byte line in each half
+        bool ok = true;
+        float corr_saved = 0.f;              // of the block whose O_j has not been taken yet
+        auto take_o = [&](int it) {          // o = o * correction + O_j of block `it`
+            ok = bar_wait(&ctrl->o_full, it & 1, &ctrl->abort) && ok;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr_saved + __uint_as_float(v[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        };
+        for (int it = 0; it < n_blk; ++it) {
+            const int key0 = (blk_lo + it) * TN;
+            ok = bar_wait(&ctrl->s_full, it & 1, &ctrl->abort) && ok;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // masks are needed on the causal edge (and with a window) only; elsewhere a row is
+            // a maximum, a multiply-add, an exp2 and an add per key
+            const bool need_mask = key0 + TN - 1 > pos0 || window > 0;
+            const int kmax = pos - key0, kmin = lo - key0;           // visible: kmin <= index <= kmax
+            // pass 1 runs while the tensor core still works on P V of the block before
+            float mx = -INFINITY;
+            if (need_mask) softmax_max<true>(tmem_s + lane_addr, kmin, kmax, mx);
+            else softmax_max<false>(tmem_s + lane_addr, kmin, kmax, mx);
+            const float m_new = fmaxf(m_run, mx * scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = ex2_approx(m_run - m_use);            // 0 on the first block
+            // that product is awaited here: its O_j is taken, and its P may be overwritten
+            if (it > 0) take_o(it - 1);
+            float lsum = 0.f;
+            if (need_mask) softmax_exp<true>(tmem_s + lane_addr, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+            else softmax_exp<false>(tmem_s + lane_addr, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+            // Slots of the last page past the context hold whatever was there before; a zero of P
+            // times a NaN would still be a NaN, so those rows of V are cleared (thread r: key r of
+            // the block; the tile has arrived, since the scores that needed K have)
+            if (key0 + r >= ctx) {
+                uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES + (size_t)r * 128);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            // the scores are out of tensor memory, P is in shared memory for the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                bar_arrive(&ctrl->s_empty);
+                bar_arrive(&ctrl->p_full);
+            }
+            l_run = l_run * corr + lsum;
+            m_run = m_new;
+            corr_saved = corr;
+        }
+        if (n_blk > 0) take_o(n_blk - 1);
+        if (ok && row_valid && n_blk > 0) {
+            const float inv = 1.0f / l_run;
+            bf16* orow = out + ((size_t)(q_start + t0 + qi) * nh + head0 + hsel) * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                uint4 pk;
+                pk.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
+                pk.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
+                pk.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
+                pk.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
+                *reinterpret_cast<uint4*>(orow + i) = pk;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    pdl_trigger();
+}
+
+// A [rows, cols] bf16 row-major matrix as a 2-D tensor map with boxes of 64 columns x box_rows rows.
+bool make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+extern "C" int rlis_attention_prefill_tc_error(void) { return tc::read_error_word(); }
+
+// Whether the tensor-core kernel takes these sizes (else the caller uses rlis_attention_prefill).
+extern "C" int rlis_attention_prefill_tc_takes(int nh, int nkv, int d, int page_size) {
+    if (d != HD || nkv <= 0 || nh % nkv != 0 || ((nh / nkv) & 1) != 0) return 0;
+    if (page_size < 8 || page_size > TN || TN % page_size != 0) return 0;
+    return 1;
+}
+
+// q, out [tokens, nh * 64]; caches [pages, nkv, page_size, 64]; tiles [n_tiles, 2] = (batch entry,
+// first token of 64) as for rlis_attention_prefill.
+extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         const int* tiles, int n_tiles, const int* cu_seqlens,
+                                         const int* ctx_lens, const int* block_tables, int max_blocks,
+                                         int n_tokens, int n_pages, int nh, int nkv, int d, int page_size,
+                                         float scale, int window, int dtype, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (dtype != RLIS_BF16 || !rlis_attention_prefill_tc_takes(nh, nkv, d, page_size) || nh / 2 > 65535)
+        return RLIS_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+          reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+        return RLIS_ERR_UNSUPPORTED;
+    const long long cache_rows = (long long)n_pages * nkv * page_size;
+    if (cache_rows >= (1ll << 31)) return RLIS_ERR_UNSUPPORTED;
+    CUtensorMap map_q, map_k, map_v;
+    if (!make_map_2d(&map_q, q, n_tokens, (long long)nh * HD, TQ) ||
+        !make_map_2d(&map_k, k_cache, cache_rows, HD, page_size) ||
+        !make_map_2d(&map_v, v_cache, cache_rows, HD, page_size))
+        return RLIS_ERR_UNSUPPORTED;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM);
+        attr_done = true;
+    }
+    rlis_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles, (unsigned)(nh / 2)), PT_THREADS, PT_SMEM, stream,
+                map_q, map_k, map_v, (bf16*)out, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv,
+                page_size, (int)cache_rows, scale, window);
+    return RLIS_LAUNCH_CHECK();
+}

@@ -176,9 +176,9 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> t
 def check_device_errors() -> None:
     """Raises if a bounded wait inside a kernel ever ran out on this device (the kernel then
     finished without its data; results since are not to be trusted).  Synchronises the device."""
-    code = lib().rlis_gemm_tcgen05_error() or lib().rlis_stream_gemm_error()
+    code = lib().rlis_gemm_tcgen05_error() or lib().rlis_stream_gemm_error() or lib().rlis_attention_prefill_tc_error()
     if code != 0:
-        raise KernelError(f"gemm_tcgen05: a bounded mbarrier wait ran out on the device (code {code})")
+        raise KernelError(f"a bounded mbarrier wait of a tcgen05 kernel ran out on the device (code {code})")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
@@ -354,6 +354,9 @@ def attention_decode_from_qkv(qkv, k_cache, v_cache, out, step, group: int, inv_
     return out
 
 
+PREFILL_TCGEN05 = True     # False: the mma.sync kernel for every size (measurements, tests of that kernel)
+
+
 def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,
                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                       window: int = 0) -> torch.Tensor:
@@ -370,6 +373,15 @@ def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, blo
     _req(block_tables, "block_tables", torch.int32, (None, None))
     if head_dim not in (64, 128) or n_heads % n_kv_heads:
         raise KernelError(f"prefill attention: head size {head_dim} is not taken (64 and 128 are)")
+    if PREFILL_TCGEN05 and lib().rlis_attention_prefill_tc_takes(n_heads, n_kv_heads, head_dim, page_size):
+        # the tcgen05 kernel: head size 64, query heads in pairs, pages that divide a block of 128 keys
+        check(lib().rlis_attention_prefill_tc(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
+            tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),
+            block_tables.shape[1], q.shape[0], k_cache.shape[0], n_heads, n_kv_heads, head_dim, page_size,
+            float(scale), int(window), _code(q.dtype), _stream()), "attention_prefill_tc")
+        _count()
+        return out
     check(lib().rlis_attention_prefill(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
         tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),

@@ -30,6 +30,8 @@ SIGNATURES = {
     "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_decode_qkv": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_prefill_tc_takes": [I, I, I, I],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
     "rlis_sample_filtered": [P, P, P, I, I, LL, P],
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
@@ -61,6 +63,8 @@ def lib():
             fn.restype = c_int
         handle.rlis_gemm_tcgen05_error.argtypes = []
         handle.rlis_gemm_tcgen05_error.restype = c_int
+        handle.rlis_attention_prefill_tc_error.argtypes = []
+        handle.rlis_attention_prefill_tc_error.restype = c_int
         handle.rlis_stream_gemm_error.argtypes = []
         handle.rlis_stream_gemm_error.restype = c_int
         handle.rlis_stream_gemm_set_target.argtypes = [c_int]

@@ -336,7 +336,8 @@ def test_decode_attention_split_over_the_context(geom, ps, splits):
     assert err <= 2e-2, err
 
 
-@pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((6, 3, 128), 16), ((4, 4, 64), 8), ((5, 1, 128), 32)])
+@pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((6, 3, 128), 16), ((4, 4, 64), 8), ((5, 1, 128), 32),
+                                     ((8, 2, 64), 8), ((4, 1, 64), 32), ((12, 6, 64), 128), ((6, 1, 64), 64)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_prefill_flash_attention_over_pages(geom, ps, window):
     """Portions of prompts of many lengths (one token short of a tile, exactly a tile, across
