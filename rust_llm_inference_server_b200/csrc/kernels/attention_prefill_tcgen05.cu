@@ -13,11 +13,13 @@
 //           past the context are asked for past the end of the tensor and arrive as zeros) into
 //           a ring of two stages, 128-byte swizzle.
 //   warp 1, one lane: S = Q K^T (tcgen05.mma, M 128, N 128, K 64) into tensor memory; after the
-//           softmax warps have written P: O_j = P V (M 128, N 64, K 128; V is the MN-major
-//           operand, straight from the cache's layout), a fresh accumulator per block.
-//   warps 2-5: a thread per row.  Two passes over its row of S in tensor memory (maximum, then
-//           exp2 and sum), P rounded to bf16 into shared memory in the swizzled K-major layout
-//           the tensor core reads; then o = o * correction + O_j in registers.
+//           softmax warps have written P: O += P V (M 128, N 64, K 128; V is the MN-major
+//           operand, straight from the cache's layout), accumulated in tensor memory.
+//   warps 2-5: a thread per row.  It takes its row of S out of tensor memory at once, finds the
+//           maximum, writes P = exp2(s - reference) rounded to bf16 into shared memory in the
+//           swizzled K-major layout the tensor core reads.  The reference follows the maximum
+//           only when that has run ahead by more than 2^8; then, rarely after the first blocks,
+//           the warp rescales its rows of O in tensor memory before the next product.
 // Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
 // other's gaps between the phases.
 //
@@ -60,9 +62,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// Both passes over a row of scores read tensor memory 32 columns at a time, and ask for the next 32
-// before they work on the ones they have: a load from tensor memory takes hundreds of cycles.
-
 template <bool MASK>
 __device__ __forceinline__ void max_of_chunk(const uint32_t (&v)[32], int c, int kmin, int kmax, float& mx) {
 #pragma unroll
@@ -71,24 +70,6 @@ __device__ __forceinline__ void max_of_chunk(const uint32_t (&v)[32], int c, int
         const float sv = __uint_as_float(v[i]);
         mx = fmaxf(mx, (!MASK || (idx <= kmax && idx >= kmin)) ? sv : -INFINITY);
     }
-}
-
-// Pass 1: the row's maximum over the visible keys.
-template <bool MASK>
-__device__ __forceinline__ void softmax_max(uint32_t taddr, int kmin, int kmax, float& mx) {
-    uint32_t va[32], vb[32];
-    tmem_ld32_nowait(taddr, va);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 32u, vb);
-    max_of_chunk<MASK>(va, 0, kmin, kmax, mx);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 64u, va);
-    max_of_chunk<MASK>(vb, 1, kmin, kmax, mx);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 96u, vb);
-    max_of_chunk<MASK>(va, 2, kmin, kmax, mx);
-    tmem_ld_wait();
-    max_of_chunk<MASK>(vb, 3, kmin, kmax, mx);
 }
 
 // P = exp2(s * scale - m) of 32 keys, rounded to bf16 into the row's line of the swizzled tile (two
@@ -106,8 +87,11 @@ __device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int
             if (!(idx <= kmax && idx >= kmin)) p0 = 0.f;
             if (!(idx + 1 <= kmax && idx + 1 >= kmin)) p1 = 0.f;
         }
-        lsum += p0 + p1;
-        pk[i] = pack_bf16(p0, p1);
+        // the sum is of the rounded values, the ones the product with V uses: the rounding of a
+        // dominant key then cancels between numerator and denominator
+        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        lsum += __low2float(h) + __high2float(h);
+        pk[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
     unsigned char* half = prow + (size_t)(c / 2) * (P_BYTES / 2);
 #pragma unroll
@@ -118,24 +102,10 @@ __device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int
     }
 }
 
-// Pass 2: P and the row's sum.
-template <bool MASK>
-__device__ __forceinline__ void softmax_exp(uint32_t taddr, int kmin, int kmax, float scale_log2, float m_use,
-                                            unsigned char* prow, int r, float& lsum) {
-    uint32_t va[32], vb[32];
-    tmem_ld32_nowait(taddr, va);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 32u, vb);
-    exp_of_chunk<MASK>(va, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 64u, va);
-    exp_of_chunk<MASK>(vb, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-    tmem_ld_wait();
-    tmem_ld32_nowait(taddr + 96u, vb);
-    exp_of_chunk<MASK>(va, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-    tmem_ld_wait();
-    exp_of_chunk<MASK>(vb, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-}
+// A row's softmax reference may lag behind its maximum by this much (in powers of two) before the
+// accumulated output is rescaled: P then holds values up to 2^8, which bf16 and the float32 sums
+// take, and the rescaling of O in tensor memory becomes rare after the first blocks.
+constexpr float RESCALE_AFTER = 8.0f;
 
 __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -194,29 +164,35 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     pdl_wait();             // q and this portion's keys come from the kernels before
 
     if (warp == 0) {
+        // producer.  A block of keys is 128 / page_size pages for K and as many for V, each a copy
+        // of its own: the lanes of the warp issue them side by side (one lane issuing sixteen
+        // copies of 2 KB a block was what bounded the kernel).
         if (lane == 0) {
             bar_expect_tx(&ctrl->q_full, Q_BYTES);
             tma_load_2d(q_tile, &map_q, head0 * HD, q_start + t0, &ctrl->q_full);
             tma_load_2d(q_tile + Q_BYTES / 2, &map_q, (head0 + 1) * HD, q_start + t0, &ctrl->q_full);
-            const int pages_per_blk = TN / page_size;
-            const int page_bytes = page_size * HD * 2;
-            for (int it = 0; it < n_blk; ++it) {
-                const int s = it % KV_STAGES;
-                if (it >= KV_STAGES && !bar_wait(&ctrl->kv_empty[s], ((it / KV_STAGES) - 1) & 1, &ctrl->abort)) break;
-                unsigned char* kt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES;
-                unsigned char* vt = kt + KV_TILE_BYTES;
-                bar_expect_tx(&ctrl->kv_full[s], 2 * KV_TILE_BYTES);
-                const int key0 = (blk_lo + it) * TN;
-                for (int p = 0; p < pages_per_blk; ++p) {
-                    const int key = key0 + p * page_size;
-                    // a page past the context, or wholly behind the window of the tile's first token
-                    // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
-                    const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
-                    const int row = wanted ? (table[key / page_size] * nkv + kvh) * page_size : cache_rows;
-                    tma_load_2d(kt + (size_t)p * page_bytes, &map_k, 0, row, &ctrl->kv_full[s]);
-                    tma_load_2d(vt + (size_t)p * page_bytes, &map_v, 0, row, &ctrl->kv_full[s]);
-                }
+        }
+        const int pages_per_blk = TN / page_size;
+        const int page_bytes = page_size * HD * 2;
+        for (int it = 0; it < n_blk; ++it) {
+            const int s = it % KV_STAGES;
+            if (it >= KV_STAGES && !bar_wait(&ctrl->kv_empty[s], ((it / KV_STAGES) - 1) & 1, &ctrl->abort)) break;
+            unsigned char* kt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES;
+            if (lane == 0) bar_expect_tx(&ctrl->kv_full[s], 2 * KV_TILE_BYTES);
+            __syncwarp();
+            const int key0 = (blk_lo + it) * TN;
+            if (lane < 2 * pages_per_blk) {
+                const int p = lane % pages_per_blk;
+                const bool is_v = lane >= pages_per_blk;
+                const int key = key0 + p * page_size;
+                // a page past the context, or wholly behind the window of the tile's first token
+                // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
+                const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
+                const int row = wanted ? (table[key / page_size] * nkv + kvh) * page_size : cache_rows;
+                tma_load_2d(kt + (is_v ? KV_TILE_BYTES : 0) + (size_t)p * page_bytes, is_v ? &map_v : &map_k, 0, row,
+                            &ctrl->kv_full[s]);
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -247,7 +223,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                     // P: two swizzled halves of 64 keys, 32 bytes a step inside a half; V: 16 keys = 2 KB further
                     const uint64_t pdesc = smem_desc_sw128(p_tile + (size_t)(k / 4) * (P_BYTES / 2)) + (uint64_t)((k % 4) * 32 >> 4);
                     const uint64_t vdesc = smem_desc_sw128(vt + (size_t)k * 16 * HD * 2);
-                    umma_bf16(tmem_o, pdesc, vdesc, IDESC_PV, k != 0 ? 1u : 0u);
+                    umma_bf16(tmem_o, pdesc, vdesc, IDESC_PV, (it | k) != 0 ? 1u : 0u);     // O accumulates over the blocks
                 }
                 umma_commit(&ctrl->o_full);
                 umma_commit(&ctrl->kv_empty[s]);
@@ -263,45 +239,77 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         const bool row_valid = qi < n_valid;
         const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;       // the reference of the exponentials so far, and their sum
         unsigned char* prow = p_tile + (size_t)r * 128;          // this row's 128-byte line in each half
         bool ok = true;
-        float corr_saved = 0.f;              // of the block whose O_j has not been taken yet
-        auto take_o = [&](int it) {          // o = o * correction + O_j of block `it`
-            ok = bar_wait(&ctrl->o_full, it & 1, &ctrl->abort) && ok;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * corr_saved + __uint_as_float(v[i]);
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        };
         for (int it = 0; it < n_blk; ++it) {
             const int key0 = (blk_lo + it) * TN;
             ok = bar_wait(&ctrl->s_full, it & 1, &ctrl->abort) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // masks are needed on the causal edge (and with a window) only; elsewhere a row is
-            // a maximum, a multiply-add, an exp2 and an add per key
+            // the whole row of scores at once, and tensor memory is free for the next block's scores
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_ld32_nowait(tmem_s + lane_addr, s0);
+            tmem_ld32_nowait(tmem_s + lane_addr + 32u, s1);
+            tmem_ld32_nowait(tmem_s + lane_addr + 64u, s2);
+            tmem_ld32_nowait(tmem_s + lane_addr + 96u, s3);
+            tmem_ld_wait();
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) bar_arrive(&ctrl->s_empty);
+            // masks are needed on the causal edge (and with a window) only
             const bool need_mask = key0 + TN - 1 > pos0 || window > 0;
             const int kmax = pos - key0, kmin = lo - key0;           // visible: kmin <= index <= kmax
-            // pass 1 runs while the tensor core still works on P V of the block before
             float mx = -INFINITY;
-            if (need_mask) softmax_max<true>(tmem_s + lane_addr, kmin, kmax, mx);
-            else softmax_max<false>(tmem_s + lane_addr, kmin, kmax, mx);
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = ex2_approx(m_run - m_use);            // 0 on the first block
-            // that product is awaited here: its O_j is taken, and its P may be overwritten
-            if (it > 0) take_o(it - 1);
+            if (need_mask) {
+                max_of_chunk<true>(s0, 0, kmin, kmax, mx);
+                max_of_chunk<true>(s1, 1, kmin, kmax, mx);
+                max_of_chunk<true>(s2, 2, kmin, kmax, mx);
+                max_of_chunk<true>(s3, 3, kmin, kmax, mx);
+            } else {
+                max_of_chunk<false>(s0, 0, kmin, kmax, mx);
+                max_of_chunk<false>(s1, 1, kmin, kmax, mx);
+                max_of_chunk<false>(s2, 2, kmin, kmax, mx);
+                max_of_chunk<false>(s3, 3, kmin, kmax, mx);
+            }
+            const float m_new = fmaxf(m_ref, mx * scale_log2);
+            // the reference moves only when the maximum has run ahead of it (always on the first keys seen)
+            const bool move = m_new - m_ref > RESCALE_AFTER || (m_ref == -INFINITY && m_new != -INFINITY);
+            float corr = 1.0f;
+            if (move) {
+                corr = ex2_approx(m_ref - m_new);                    // 0 when nothing was seen before
+                m_ref = m_new;
+                l_run *= corr;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // the product P V of the block before: P may be overwritten and O rescaled once it is done
+            if (it > 0) {
+                ok = bar_wait(&ctrl->o_full, (it - 1) & 1, &ctrl->abort) && ok;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, move)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
+                    }
+                    tmem_st_wait();
+                }
+            }
             float lsum = 0.f;
-            if (need_mask) softmax_exp<true>(tmem_s + lane_addr, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-            else softmax_exp<false>(tmem_s + lane_addr, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+            if (need_mask) {
+                exp_of_chunk<true>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<true>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<true>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<true>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+            } else {
+                exp_of_chunk<false>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<false>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<false>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                exp_of_chunk<false>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+            }
+            l_run += lsum;
             // Slots of the last page past the context hold whatever was there before; a zero of P
             // times a NaN would still be a NaN, so those rows of V are cleared (thread r: key r of
             // the block; the tile has arrived, since the scores that needed K have)
@@ -310,30 +318,32 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
 #pragma unroll
                 for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
             }
-            // the scores are out of tensor memory, P is in shared memory for the tensor core
+            // P is in shared memory for the tensor core, O (if rescaled) back in tensor memory
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                bar_arrive(&ctrl->s_empty);
-                bar_arrive(&ctrl->p_full);
-            }
-            l_run = l_run * corr + lsum;
-            m_run = m_new;
-            corr_saved = corr;
+            if (lane == 0) bar_arrive(&ctrl->p_full);
         }
-        if (n_blk > 0) take_o(n_blk - 1);
-        if (ok && row_valid && n_blk > 0) {
+        if (n_blk > 0) {
+            ok = bar_wait(&ctrl->o_full, (n_blk - 1) & 1, &ctrl->abort) && ok;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l_run;
             bf16* orow = out + ((size_t)(q_start + t0 + qi) * nh + head0 + hsel) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
+                if (ok && row_valid) {
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                uint4 pk;
-                pk.x = pack_bf16(o[i] * inv, o[i + 1] * inv);
-                pk.y = pack_bf16(o[i + 2] * inv, o[i + 3] * inv);
-                pk.z = pack_bf16(o[i + 4] * inv, o[i + 5] * inv);
-                pk.w = pack_bf16(o[i + 6] * inv, o[i + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + i) = pk;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 pk;
+                        pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                        pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                        pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = pk;
+                    }
+                }
             }
         }
     }
