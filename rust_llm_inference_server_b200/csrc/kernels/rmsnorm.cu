@@ -85,14 +85,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restri
     const size_t obase = (size_t)blockIdx.x * hidden;
     const size_t base = rows != nullptr ? (size_t)rows[blockIdx.x] * hidden : obase;
     const int nvec = hidden >> 2;
-    float4 v[MAXV], wv[MAXV];
-    // the norm's weight and the row list are written by no kernel of the step: read them while
-    // the kernel before is still running
-#pragma unroll
-    for (int it = 0; it < MAXV; ++it) {
-        const int i = it * blockDim.x + threadIdx.x;
-        if (i < nvec) wv[it] = *reinterpret_cast<const float4*>(w + 4 * (size_t)i);
-    }
+    float4 v[MAXV];
     pdl_wait_and_trigger();
     float ss = 0.f;
 #pragma unroll
@@ -118,7 +111,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ resid, const T* __restri
     for (int it = 0; it < MAXV; ++it) {
         const int i = it * blockDim.x + threadIdx.x;
         if (i < nvec) {
-            const float4 ww = wv[it];
+            const float4 ww = *reinterpret_cast<const float4*>(w + 4 * (size_t)i);
             const float4 x = v[it];
             Delta4<T>::store(out + obase + 4 * (size_t)i,
                              make_float4(x.x * rstd * ww.x, x.y * rstd * ww.y, x.z * rstd * ww.z, x.w * rstd * ww.w));
