@@ -201,3 +201,38 @@ def test_bad_configurations_and_requests_are_refused():
     s = sched(8)
     with pytest.raises(ValueError):
         s.add(0, [])
+
+
+def test_a_step_ahead_with_placeholders_registers_the_real_tokens():
+    """The engine's decode-ahead: a placeholder is appended for the token still on the device, the
+    next step is scheduled on it, the value arrives later, and only then is the step's progress
+    recorded, so that a page it fills enters the prefix registry under its real tokens."""
+    s = sched(32, prefix=True, block_size=4)
+    prompt = toks(1, 6)
+    s.add(0, prompt)
+    (seqs, _) = s.schedule()
+    assert [tuple(x) for x in seqs] == [(0, 0, 6)]
+    s.advance(0, 6)
+    # the token sampled by that step is still on the device: schedule the next step on a placeholder
+    s.append_token(0, 0)
+    (seqs, pre) = s.schedule()
+    assert [tuple(x) for x in seqs] == [(0, 6, 7)] and not pre
+    assert s.tokens(0, 6, 7) == [0]
+    s.set_token(0, 6, 41)                                 # it arrives
+    assert s.tokens(0, 0, 7) == prompt + [41]
+    s.append_token(0, 0)                                  # and the step after is launched on the next placeholder
+    s.advance(0, 7)
+    (seqs, _) = s.schedule()
+    assert [tuple(x) for x in seqs] == [(0, 7, 8)]
+    s.set_token(0, 7, 42)
+    s.advance(0, 8)                                       # the second page (tokens 4..7) is full: registered as 41, 42
+    with pytest.raises(IndexError):
+        s.set_token(0, 99, 1)
+    s.set_token(12345, 0, 1)                              # an unknown request (finished meanwhile): ignored
+    s.remove(0)
+    # a second request with the same eight tokens finds both pages
+    s.add(1, prompt + [41, 42, 5])
+    (seqs, _) = s.schedule()
+    assert [tuple(x) for x in seqs] == [(1, 8, 9)] and s.cached_tokens() == 8
+    # had the page been registered with the placeholder, this request would have found one page only
+    assert s.check() == ""
