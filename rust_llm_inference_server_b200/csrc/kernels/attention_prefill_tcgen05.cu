@@ -23,6 +23,10 @@
 // Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
 // other's gaps between the phases.
 //
+// (Measured at 8192 tokens, 32:8 heads, pages of 16: 706 us, 389 TFLOP/s; the mma.sync kernel
+// 1356 us.  One lane issuing a block's sixteen page copies: 972 us whatever the softmax warps did.
+// Eight softmax warps, two threads a row with a softmax stream and an accumulator each: 822 us.)
+//
 // Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets the error word
 // (rlis_attention_prefill_tc_error), every role runs to its end without further waits, and the
 // CTA frees its tensor memory before it returns.
