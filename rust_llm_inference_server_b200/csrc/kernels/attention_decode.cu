@@ -15,8 +15,7 @@
 //
 // Scratch: when splits > 1 the kernel writes partial results [request, head, split, d + 2] float32
 // to a caller-provided buffer and `attention_decode_combine` merges them.
-#include "common.cuh"
-#include "mma_utils.cuh"
+#include "tcgen05_utils.cuh"
 #include <math.h>
 
 namespace {
@@ -198,8 +197,13 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_kernel(
 // the HBM rate; here the heads of a group are the rows of an m16n8k16 tile, so a key costs a few
 // tensor instructions and the kernel waits on memory only.
 //
-// Per warp: blocks of 32 keys, double-buffered in shared memory by 16-byte asynchronous copies
-// (rows padded to D + 8 elements, which keeps ldmatrix free of bank conflicts).
+// Per warp: blocks of 32 keys in a ring of 2 to 4 stages in shared memory.  Head size 64 (TMA):
+// a block is one to four bulk tensor copies of the cache seen as a [rows, 64] tensor (a page, or 32
+// rows of one), 128-byte swizzle, an mbarrier per stage and warp; ldmatrix XORs the 16-byte chunk
+// index with the row's index in its group of 8.  Otherwise 16-byte asynchronous copies into rows
+// padded to D + 8 elements.  (The 16-byte copies stopped at 4.9 TB/s with 96 KB in flight an SM,
+// and more stages did not help them; the bulk copies reach 5.65 TB/s at batch 64 and take 14.2
+// instead of 17.4 us at batch 8.)
 //   S[heads x 32 keys] = Q K^T      (K rows through ldmatrix, bf16 products, float32 sums)
 //   online softmax in float32 on S * scale
 //   O[heads x D]      += P V        (P rounded to bf16 as the A operand, V through ldmatrix.trans)
@@ -220,8 +224,9 @@ struct DecodeQkv {
 constexpr int DEC_TABLE_SLOTS = 512;      // block-table entries of a CTA kept in shared memory (2 KB: three CTAs of head size 64 still fit an SM)
 
 
-template <int D, int NSTAGE>
+template <int D, int NSTAGE, bool TMA>
 __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int cache_rows,
     const bf16* __restrict__ q, const bf16* k_cache, const bf16* v_cache,
     bf16* __restrict__ out, float* __restrict__ partial, const int* __restrict__ dec_rows,
     const int* __restrict__ dec_seqs, const int* __restrict__ ctx_lens,
@@ -230,15 +235,30 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     __shared__ int s_last;
     __shared__ float s_cos[D / 2], s_sin[D / 2];
     __shared__ int s_table[DEC_TABLE_SLOTS];
-    constexpr int STRIDE = D + 8;            // elements per padded row
+    __shared__ uint64_t s_full[DEC_WARPS][NSTAGE];     // TMA: a stage of a warp has arrived
+    __shared__ int s_abort;
+    // TMA (head size 64): rows of 128 bytes, the 128-byte swizzle instead of padding
+    constexpr int STRIDE = TMA ? D : D + 8;  // elements per row
     constexpr int KS = D / 16;               // k-steps of Q K^T
     constexpr int ND = D / 8;                // n-tiles of P V
     constexpr int CPR = D / 8;               // 16-byte chunks per row
     constexpr int TILE = 32 * STRIDE;        // elements of one K or V tile
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * NSTAGE * 2 * TILE;   // [stage][K|V][32][STRIDE]
+    if (TMA) {
+        if ((smem_u32(smem_raw) & 1023u) != 0u) {      // the swizzled tiles need it; checked, never seen
+            if (threadIdx.x == 0) atomicExch(&tc::g_tc_error, 2);
+            return;
+        }
+        if (threadIdx.x == 0) s_abort = 0;
+        if (lane == 0) {
+            for (int i = 0; i < NSTAGE; ++i) tc::bar_init(&s_full[warp][i], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
 
     const int kvh = blockIdx.x, bi = blockIdx.y, split = blockIdx.z;
     const int row = dec_rows[bi];
@@ -272,9 +292,36 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     }
     const int key_in0 = lane / CPR, c16 = lane % CPR;       // chunk i of a lane: key_in0 + i * (32 / CPR)
     const uint32_t sm_off0 = (uint32_t)(key_in0 * STRIDE + c16 * 8);
+    // TMA: a block of 32 keys is 32 / min(page, 32) boxes of the cache seen as [rows, 64]; a box
+    // wholly past the context or behind the window is asked for past the end of the tensor and
+    // arrives as zeros.  One lane announces the bytes, then a lane per box issues its copy.
+    const int box_rows = page_size < 32 ? page_size : 32;
+    const int boxes = 32 / box_rows;
     auto issue = [&](int blk, int stage) {
         bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
         bf16* vs_ = ks_ + TILE;
+        if (TMA) {
+            // the tile was read by ldmatrix until a moment ago: order those reads before the copy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::bar_expect_tx(&s_full[warp][stage], 2 * 32 * D * 2);
+            __syncwarp();
+            if (lane < 2 * boxes) {
+                const int bx = lane % boxes;
+                const bool is_v = lane >= boxes;
+                const int key = (blk << 5) + bx * box_rows;
+                const bool wanted = key < ctx && key + box_rows > lo_all;
+                int rowc = cache_rows;
+                if (wanted) {
+                    const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+                    const int in_page = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+                    const int page = table_in_smem ? s_table[pi - page0] : table[pi];
+                    rowc = (page * nkv + kvh) * page_size + in_page;
+                }
+                tc::tma_load_2d((is_v ? vs_ : ks_) + (size_t)bx * box_rows * D, is_v ? &map_v : &map_k, 0, rowc,
+                                &s_full[warp][stage]);
+            }
+        } else {
 #pragma unroll
         for (int i = 0; i < CPR; ++i) {               // 32 * CPR chunks, 32 lanes
             const int key_in = key_in0 + i * (32 / CPR);
@@ -292,6 +339,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             cp_async16(vs_ + so, vbase + off, valid);
         }
         cp_async_commit();
+        }
     };
 
     // scores are kept in units of log2(e) (s * scale * log2 e): exp becomes a single exp2
@@ -336,7 +384,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         if (i < deferred_from) continue;
         const int b = blk + i * DEC_WARPS;
         if (b < blk1) issue(b, i);
-        else cp_async_commit();
+        else if (!TMA) cp_async_commit();
     }
 
     // Q as A fragments: row g = head g of the group (rows >= nrep and rows 8..15 are zero)
@@ -372,18 +420,32 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
         }
     }
 
+    int turn = 0;                              // blocks this warp has worked on: block i sits in stage i % NSTAGE
+    bool arrived = true;
     while (blk < blk1) {
         const int nblk = blk + DEC_WARPS;
         {
             const int ahead = blk + (NSTAGE - 1) * DEC_WARPS;
             const int st = stage == 0 ? NSTAGE - 1 : stage - 1;       // the stage worked on last turn
             if (ahead < blk1) issue(ahead, st);
-            else cp_async_commit();
-            cp_async_wait<NSTAGE - 1>();
+            else if (!TMA) cp_async_commit();
+            if (TMA) arrived = tc::bar_wait(&s_full[warp][stage], (uint32_t)(turn / NSTAGE) & 1u, &s_abort) && arrived;
+            else cp_async_wait<NSTAGE - 1>();
         }
+        ++turn;
         __syncwarp();
         const bf16* ks_ = wbase + (size_t)stage * 2 * TILE;
         const bf16* vs_ = ks_ + TILE;
+        if (TMA && (blk << 5) + 31 >= ctx) {
+            // slots of the last page past the context hold whatever was there before; a zero of P
+            // times a NaN would still be a NaN: those rows of V are cleared (a lane per row)
+            if ((blk << 5) + lane >= ctx) {
+                uint4* vr = reinterpret_cast<uint4*>(const_cast<bf16*>(vs_) + lane * STRIDE);
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
         if (fused && fz.slots != nullptr && blk == newest_blk) {
             // the request's newest key and value: from the projection into this tile and into the cache
             const int r = (ctx - 1) & 31;
@@ -394,15 +456,17 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (size_t)(slot % page_size)) * D;
             bf16* kt = const_cast<bf16*>(ks_) + r * STRIDE;
             bf16* vt = const_cast<bf16*>(vs_) + r * STRIDE;
+            // where element j of row r sits: with the swizzle, its 16-byte chunk is XORed with r % 8
+            auto at_el = [&](int j) { return TMA ? ((((j >> 3) ^ (r & 7)) << 3) | (j & 7)) : j; };
             for (int j = lane; j < D / 2; j += 32) {
                 const float a = __bfloat162float(krow[j]), b = __bfloat162float(krow[j + D / 2]);
                 const bf16 k1 = from_f<bf16>(rope_first(a, b, s_cos[j], s_sin[j]));
                 const bf16 k2 = from_f<bf16>(rope_second(a, b, s_cos[j], s_sin[j]));
                 const bf16 v1 = vrow[j], v2 = vrow[j + D / 2];
-                kt[j] = k1;
-                kt[j + D / 2] = k2;
-                vt[j] = v1;
-                vt[j + D / 2] = v2;
+                kt[at_el(j)] = k1;
+                kt[at_el(j + D / 2)] = k2;
+                vt[at_el(j)] = v1;
+                vt[at_el(j + D / 2)] = v2;
                 fz.k_cache[at + j] = k1;
                 fz.k_cache[at + j + D / 2] = k2;
                 fz.v_cache[at + j] = v1;
@@ -420,7 +484,9 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 #pragma unroll
             for (int ks2 = 0; ks2 < KS / 2; ++ks2) {
                 uint32_t kb[4];
-                ldmatrix_x4(kb, ks_ + (nt * 8 + (lane & 7)) * STRIDE + ks2 * 32 + (lane >> 3) * 8);
+                // (swizzle: the 16-byte chunk index is XORed with the row's index in its group of 8)
+                const int kchunk = ks2 * 4 + (lane >> 3);
+                ldmatrix_x4(kb, ks_ + (nt * 8 + (lane & 7)) * STRIDE + ((TMA ? kchunk ^ (lane & 7) : kchunk) << 3));
                 mma_bf16_16816(sacc[nt], qa[2 * ks2], kb[0], kb[1]);
                 mma_bf16_16816(sacc[nt], qa[2 * ks2 + 1], kb[2], kb[3]);
             }
@@ -470,7 +536,8 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             for (int nd2 = 0; nd2 < ND / 2; ++nd2) {
                 uint32_t vb[4];
                 const int mat = lane >> 3;
-                ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * STRIDE + (nd2 * 2 + (mat >> 1)) * 8);
+                const int vchunk = nd2 * 2 + (mat >> 1);
+                ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * STRIDE + ((TMA ? vchunk ^ (lane & 7) : vchunk) << 3));
                 mma_bf16_16816(oacc[2 * nd2], pa, vb[0], vb[1]);
                 mma_bf16_16816(oacc[2 * nd2 + 1], pa, vb[2], vb[3]);
             }
@@ -617,11 +684,12 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
 constexpr int kMaxTickets = 65536;
 __device__ int g_decode_tickets[kMaxTickets];
 
+int g_decode_tma = 1;        // 0: 16-byte asynchronous copies for every size (measurements)
 int g_decode_cluster = 1;    // 0: merge through global memory and tickets even where a cluster could (measurements)
 int g_decode_stages = 0;     // 0: chosen from the grid; 2..4 for measurements (rlis_attention_decode_set_stages)
 
-template <int D, int NSTAGE> constexpr size_t decode_mma_smem_bytes() {
-    return (size_t)DEC_WARPS * NSTAGE * 2 * 32 * (D + 8) * sizeof(bf16);
+template <int D, int NSTAGE, bool TMA> constexpr size_t decode_mma_smem_bytes() {
+    return (size_t)DEC_WARPS * NSTAGE * 2 * 32 * (TMA ? D : D + 8) * sizeof(bf16);
 }
 
 // Merges the splits: big = max m over non-empty splits, w = exp(m - big),
@@ -658,6 +726,8 @@ size_t decode_smem_bytes(int nrep, int d) {
 // Floats of scratch that `rlis_attention_decode` needs for these sizes (0 when splits == 1).
 extern "C" void rlis_attention_decode_set_stages(int stages) { g_decode_stages = stages; }
 extern "C" void rlis_attention_decode_set_cluster(int on) { g_decode_cluster = on; }
+extern "C" void rlis_attention_decode_set_tma(int on) { g_decode_tma = on; }
+extern "C" int rlis_attention_decode_error(void) { return tc::read_error_word(); }
 
 
 extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, int d, int splits) {
@@ -668,7 +738,7 @@ namespace {
 int decode_launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* partial,
                   const int* dec_rows, const int* dec_seqs, const int* ctx_lens, const int* block_tables,
                   int max_blocks, int n_decode, int nh, int nkv, int d, int page_size, float scale,
-                  int window, int splits, int dtype, cudaStream_t stream, const DecodeQkv& fz) {
+                  int window, int splits, int dtype, cudaStream_t stream, const DecodeQkv& fz, int n_pages) {
     if (n_decode <= 0) return 0;
     if (dtype != RLIS_BF16 || d % 8 != 0 || d > 256 || d < 8 || nkv <= 0 || nh % nkv != 0 || splits < 1)
         return RLIS_ERR_UNSUPPORTED;
@@ -706,31 +776,49 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
         int stages = g_decode_stages;
         if (stages == 0) stages = ctas <= sms ? 4 : (ctas <= 2 * sms ? 3 : 2);
         if (d == 128 && stages > 3) stages = 3;               // 4 stages of 128-wide rows do not fit
-#define LAUNCH_MMA(DD, NS)                                                                             \
+        // Head size 64 with pages of 8 tokens or more (that divide, or are divided by, a block of 32
+        // keys): the keys come by bulk tensor copies into swizzled tiles.  Needs the number of pages
+        // (the tensor's bounds); without it, and for the other sizes, 16-byte asynchronous copies.
+        const long long cache_rows = (long long)n_pages * nkv * page_size;
+        bool tma = g_decode_tma && d == 64 && n_pages > 0 && page_size >= 8 &&
+                   (32 % page_size == 0 || page_size % 32 == 0) && cache_rows < (1ll << 31) &&
+                   ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+        CUtensorMap map_k = {}, map_v = {};
+        if (tma) {
+            const int box_rows = page_size < 32 ? page_size : 32;
+            tma = tc::make_map(&map_k, k_cache, (int)cache_rows, 64, box_rows) &&
+                  tc::make_map(&map_v, v_cache, (int)cache_rows, 64, box_rows);
+        }
+#define LAUNCH_MMA(DD, NS, TM)                                                                         \
     do {                                                                                               \
         static bool attr_done = false;                                                                 \
         if (!attr_done) {                                                                              \
-            cudaFuncSetAttribute(attn_decode_mma_kernel<DD, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 (int)decode_mma_smem_bytes<DD, NS>());                                \
+            cudaFuncSetAttribute(attn_decode_mma_kernel<DD, NS, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)decode_mma_smem_bytes<DD, NS, TM>());                            \
             attr_done = true;                                                                          \
         }                                                                                              \
         if (cluster)                                                                                   \
-            rlis_launch_cluster(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), \
-                stream, dim3(1, 1, (unsigned)splits),                                                  \
+            rlis_launch_cluster(attn_decode_mma_kernel<DD, NS, TM>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS, TM>(), \
+                stream, dim3(1, 1, (unsigned)splits), map_k, map_v, (int)cache_rows,                   \
                 (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
                 ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz, 1); \
         else                                                                                           \
-            rlis_launch(attn_decode_mma_kernel<DD, NS>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS>(), stream, \
+            rlis_launch(attn_decode_mma_kernel<DD, NS, TM>, grid, DEC_THREADS, decode_mma_smem_bytes<DD, NS, TM>(), stream, \
+                map_k, map_v, (int)cache_rows,                                                         \
                 (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows, dec_seqs, \
                 ctx_lens, block_tables, max_blocks, nh, nkv, nrep, page_size, scale, window, splits, tickets, fz, 0); \
     } while (0)
-        if (d == 64) {
-            if (stages >= 4) LAUNCH_MMA(64, 4);
-            else if (stages == 3) LAUNCH_MMA(64, 3);
-            else LAUNCH_MMA(64, 2);
+        if (d == 64 && tma) {
+            if (stages >= 4) LAUNCH_MMA(64, 4, true);
+            else if (stages == 3) LAUNCH_MMA(64, 3, true);
+            else LAUNCH_MMA(64, 2, true);
+        } else if (d == 64) {
+            if (stages >= 4) LAUNCH_MMA(64, 4, false);
+            else if (stages == 3) LAUNCH_MMA(64, 3, false);
+            else LAUNCH_MMA(64, 2, false);
         } else {
-            if (stages >= 3) LAUNCH_MMA(128, 3);
-            else LAUNCH_MMA(128, 2);
+            if (stages >= 3) LAUNCH_MMA(128, 3, false);
+            else LAUNCH_MMA(128, 2, false);
         }
 #undef LAUNCH_MMA
         launched = true;
@@ -767,7 +855,20 @@ extern "C" int rlis_attention_decode(const void* q, const void* k_cache, const v
                                      int splits, int dtype, cudaStream_t stream) {
     const DecodeQkv none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     return decode_launch(q, k_cache, v_cache, out, partial, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks,
-                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, none);
+                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, none, 0);
+}
+
+// The same with the number of pages of the caches [pages, nkv, page_size, d], which lets the kernel
+// fetch keys by bulk tensor copies (see decode_launch).
+extern "C" int rlis_attention_decode_pages(const void* q, const void* k_cache, const void* v_cache,
+                                           void* out, float* partial, const int* dec_rows,
+                                           const int* dec_seqs, const int* ctx_lens,
+                                           const int* block_tables, int max_blocks, int n_decode, int nh,
+                                           int nkv, int d, int page_size, int n_pages, float scale, int window,
+                                           int splits, int dtype, cudaStream_t stream) {
+    const DecodeQkv none = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    return decode_launch(q, k_cache, v_cache, out, partial, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks,
+                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, none, n_pages);
 }
 
 // The same for a step that decodes only, straight from the q|k|v projection [tokens, (nh + 2 nkv) d]
@@ -778,12 +879,12 @@ extern "C" int rlis_attention_decode_qkv(const void* qkv, const int* positions, 
                                          const float* inv_freq, void* k_cache, void* v_cache, void* out,
                                          float* partial, const int* dec_rows, const int* dec_seqs,
                                          const int* ctx_lens, const int* block_tables, int max_blocks,
-                                         int n_decode, int nh, int nkv, int d, int page_size, float scale,
-                                         int window, int splits, int dtype, cudaStream_t stream) {
+                                         int n_decode, int nh, int nkv, int d, int page_size, int n_pages,
+                                         float scale, int window, int splits, int dtype, cudaStream_t stream) {
     if (qkv == nullptr || positions == nullptr) return RLIS_ERR_UNSUPPORTED;
     const DecodeQkv fz = {(const bf16*)qkv, positions, slots, inv_freq, (bf16*)k_cache, (bf16*)v_cache};
     return decode_launch(nullptr, k_cache, v_cache, out, partial, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks,
-                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, fz);
+                         n_decode, nh, nkv, d, page_size, scale, window, splits, dtype, stream, fz, n_pages);
 }
 
 // ------------------------------------------------------------------------------------------

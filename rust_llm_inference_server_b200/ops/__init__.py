@@ -176,7 +176,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> t
 def check_device_errors() -> None:
     """Raises if a bounded wait inside a kernel ever ran out on this device (the kernel then
     finished without its data; results since are not to be trusted).  Synchronises the device."""
-    code = lib().rlis_gemm_tcgen05_error() or lib().rlis_stream_gemm_error() or lib().rlis_attention_prefill_tc_error()
+    code = (lib().rlis_gemm_tcgen05_error() or lib().rlis_stream_gemm_error() or lib().rlis_attention_prefill_tc_error()
+            or lib().rlis_attention_decode_error())
     if code != 0:
         raise KernelError(f"a bounded mbarrier wait of a tcgen05 kernel ran out on the device (code {code})")
 
@@ -304,12 +305,12 @@ def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, blo
         need = n * n_heads * splits * (head_dim + 2)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"decode attention: scratch of {need} float32 elements is needed")
-    check(lib().rlis_attention_decode(
+    check(lib().rlis_attention_decode_pages(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         scratch.data_ptr() if splits > 1 else None, dec_rows.data_ptr(), dec_seqs.data_ptr(),
         ctx_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n, n_heads,
-        n_kv_heads, head_dim, page_size, float(scale), int(window), int(splits), _code(q.dtype),
-        _stream()), "attention_decode")
+        n_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), int(splits),
+        _code(q.dtype), _stream()), "attention_decode")
     _count()
     return out
 
@@ -348,7 +349,8 @@ def attention_decode_from_qkv(qkv, k_cache, v_cache, out, step, group: int, inv_
         inv_freq.data_ptr() if inv_freq is not None else None, k_cache.data_ptr(), v_cache.data_ptr(),
         out.data_ptr(), scratch.data_ptr() if splits > 1 else None, step.dec_rows.data_ptr(),
         step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n, n_heads,
-        n_kv_heads, head_dim, page_size, float(scale), int(window), int(splits), _code(qkv.dtype), _stream()),
+        n_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), int(splits),
+        _code(qkv.dtype), _stream()),
         "attention_decode_qkv")
     _count()
     return out

@@ -28,7 +28,8 @@ SIGNATURES = {
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
-    "rlis_attention_decode_qkv": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
+    "rlis_attention_decode_pages": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
+    "rlis_attention_decode_qkv": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
     "rlis_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_prefill_tc_takes": [I, I, I, I],
@@ -71,6 +72,10 @@ def lib():
         handle.rlis_stream_gemm_set_target.restype = None
         handle.rlis_attention_decode_set_stages.argtypes = [c_int]
         handle.rlis_attention_decode_set_stages.restype = None
+        handle.rlis_attention_decode_set_tma.argtypes = [c_int]
+        handle.rlis_attention_decode_set_tma.restype = None
+        handle.rlis_attention_decode_error.argtypes = []
+        handle.rlis_attention_decode_error.restype = c_int
         handle.rlis_attention_decode_set_cluster.argtypes = [c_int]
         handle.rlis_attention_decode_set_cluster.restype = None
         handle.rlis_set_pdl.argtypes = [c_int]
