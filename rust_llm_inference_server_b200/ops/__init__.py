@@ -279,8 +279,13 @@ def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
     if groups * 4 > DECODE_CLUSTER_MAX_CTAS:
         want = max(want, min(4, max_ctx // 512))
     want = max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 32))
-    if 1 < want < 16 and groups * min(want, 8) <= DECODE_CLUSTER_MAX_CTAS:
-        want = 1 << (min(want, 8).bit_length() - 1)
+    if want > 1 and groups * min(want, 8) <= DECODE_CLUSTER_MAX_CTAS:
+        # merged inside a cluster: 2, 4 or 8 pieces; with few requests 8, until a piece gets long
+        # (batch 1, context 4096: 6.7 us with 8 pieces in a cluster, 12.6 us with 32 and tickets)
+        pieces = 1 << (min(want, 8).bit_length() - 1)
+        while 8 <= pieces < 32 and want >= 2 * pieces and max_ctx // pieces > 1536:
+            pieces *= 2
+        want = pieces
     return want
 
 
