@@ -192,8 +192,15 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         cluster_sync_all();
 #pragma unroll 1
         for (int t = split; t < M; t += splits) {
+            // all loads are issued before the first sum needs one (a sum right behind its load would
+            // make the trips through the cluster one after the other); summed in split order
+            float pv[MAX_SPLITS];
+#pragma unroll
+            for (int s = 0; s < MAX_SPLITS; ++s)
+                pv[s] = s < splits ? ld_dsmem(part + t * SF + (int)threadIdx.x, (uint32_t)s) : 0.f;
             float v = 0.f;
-            for (int s = 0; s < splits; ++s) v += ld_dsmem(part + t * SF + (int)threadIdx.x, (uint32_t)s);
+#pragma unroll
+            for (int s = 0; s < MAX_SPLITS; ++s) v += pv[s];
             if (ok) store_token<EPI, OutT>(y, v, t, f, lane, N);
         }
         cluster_sync_all();        // nobody leaves while its shared memory may still be read
