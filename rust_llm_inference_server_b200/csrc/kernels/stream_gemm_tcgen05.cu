@@ -13,11 +13,11 @@
 //   * four warps read the accumulator (a lane = a feature, a column = a token) and store.
 // Matrices with few features would fill few SMs, so k is split over the CTAs of a thread-block
 // cluster (grid = feature tiles x splits, 2 to 16 splits, more CTAs than SMs and all resident at
-// once: the whole matrix is requested in the first microsecond).  Each CTA of the cluster leaves
-// its float32 partial sums in its own shared memory; after a cluster barrier CTA r adds, for the
-// tokens r, r + splits, ..., the partial sums of all CTAs through distributed shared memory in
-// the order of the splits, so the result does not depend on timing and nothing passes through
-// global memory.  The number of splits depends on N and K only, never on the rows, so a token's
+// once: the whole matrix is requested in the first microsecond).  After a cluster barrier (all
+// products done, the stages free) each CTA sends its float32 partial sums of token t into the
+// shared memory of CTA t % splits (st.async, counted on that CTA's mbarrier), which adds the rows
+// it was sent in the order of the splits: the result does not depend on timing, nothing passes
+// through global memory, and no CTA waits for another one at the end.  The number of splits depends on N and K only, never on the rows, so a token's
 // result does not depend on its neighbours.
 //
 // The first stages of W are requested before the kernel waits for its predecessor in the stream
@@ -59,9 +59,20 @@ struct SCtrl {
     uint64_t full[S_STAGES];
     uint64_t empty[S_STAGES];
     uint64_t acc_full;
+    uint64_t red_full;      // the partial sums of the tokens this CTA finishes have arrived from the cluster
     uint32_t tmem_base;
     int abort;
 };
+
+// A float into the shared memory of the cluster's CTA `rank` (at the offset of `local`), counted
+// on that CTA's mbarrier (at the offset of `bar`).
+__device__ __forceinline__ void st_async_f32(float* local, float v, uint64_t* bar, uint32_t rank) {
+    uint32_t raddr, rbar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(raddr), "r"(__float_as_uint(v)), "r"(rbar) : "memory");
+}
 
 template <int EPI, typename OutT>
 __device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t, int f, int lane, int N) {
@@ -104,7 +115,14 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
             bar_init(&ctrl->empty[s], 1);
         }
         bar_init(&ctrl->acc_full, 1);
+        bar_init(&ctrl->red_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // tokens split, split + splits, ... are finished by this CTA: every CTA of the cluster
+        // sends a row of 128 floats for each of them
+        const int owned = split < M ? (M - split + splits - 1) / splits : 0;
+        if (splits > 1 && owned > 0) bar_expect_tx(&ctrl->red_full, (uint32_t)(owned * splits * SF * 4));
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     }
     if (warp == 2) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctrl->tmem_base)), "r"(TMEM_COLS) : "memory");
@@ -172,9 +190,13 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                 if (c * 16 + j < M) store_token<EPI, OutT>(y, __uint_as_float(r[j]), c * 16 + j, f, lane, N);
         }
     } else {
-        // all products of this CTA are done, so the stages are free: the partial sums go there,
-        // [token][feature of the tile]
+        // Once every CTA of the cluster is done with its products, the stages are free everywhere:
+        // each CTA sends its partial sums of token t to the CTA that finishes t (rank t % splits),
+        // into that CTA's stages as [t / splits][sender][feature], counted on its mbarrier.  The
+        // finisher waits for its bytes only, adds the rows in the order of the splits, and nobody
+        // reads anybody's shared memory, so nobody has to be waited for at the end.
         float* part = reinterpret_cast<float*>(w_tiles);
+        cluster_sync_all();
 #pragma unroll 1
         for (int c = 0; c < NT / 16; ++c) {
             if (c * 16 >= M) break;
@@ -186,24 +208,22 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                 for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (c * 16 + j < M) part[(c * 16 + j) * SF + (int)threadIdx.x] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) {
+                const int t = c * 16 + j;
+                if (t < M)
+                    st_async_f32(part + ((t / splits) * splits + split) * SF + (int)threadIdx.x, __uint_as_float(r[j]),
+                                 &ctrl->red_full, (uint32_t)(t % splits));
+            }
         }
-        cluster_sync_all();
+        if (split < M) {
+            const bool got = bar_wait(&ctrl->red_full, 0, &ctrl->abort);
 #pragma unroll 1
-        for (int t = split; t < M; t += splits) {
-            // all loads are issued before the first sum needs one (a sum right behind its load would
-            // make the trips through the cluster one after the other); summed in split order
-            float pv[MAX_SPLITS];
-#pragma unroll
-            for (int s = 0; s < MAX_SPLITS; ++s)
-                pv[s] = s < splits ? ld_dsmem(part + t * SF + (int)threadIdx.x, (uint32_t)s) : 0.f;
-            float v = 0.f;
-#pragma unroll
-            for (int s = 0; s < MAX_SPLITS; ++s) v += pv[s];
-            if (ok) store_token<EPI, OutT>(y, v, t, f, lane, N);
+            for (int t = split, slot = 0; t < M; t += splits, ++slot) {
+                float v = 0.f;
+                for (int s = 0; s < splits; ++s) v += part[(slot * splits + s) * SF + (int)threadIdx.x];
+                if (ok && got) store_token<EPI, OutT>(y, v, t, f, lane, N);
+            }
         }
-        cluster_sync_all();        // nobody leaves while its shared memory may still be read
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
