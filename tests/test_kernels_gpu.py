@@ -530,3 +530,30 @@ def test_filtered_sampling_on_the_device_equals_the_plain_rule():
     ids = ops.sample_filtered(small, torch.from_numpy(ps_.view(np.int32)).cuda()).cpu().numpy()
     freq = np.bincount(ids, minlength=6) / 6000
     assert np.abs(freq - P.filtered_distribution(np.array([0.0, 1.0, 2.0, -1.0, 0.5, 1.5], np.float32), 0.7, 4, 0.8)).max() < 0.03
+
+
+def test_decode_attention_over_long_contexts():
+    """Contexts of tens of thousands of keys: pieces whose slice of the block table no longer fits
+    the kernel's shared-memory copy (it then reads the table from global memory), few and many
+    pieces, against the float32 kernel for any query length."""
+    from rust_llm_inference_server_b200 import ops
+    torch.manual_seed(0)
+    nh, nkv, d, ps = 8, 2, 64, 16
+    B, ctx = 2, 20000
+    n_pages = B * (ctx // ps + 1)
+    kc = (torch.randn(n_pages, nkv, ps, d, device="cuda") * 0.5).bfloat16()
+    vc = (torch.randn(n_pages, nkv, ps, d, device="cuda") * 0.5).bfloat16()
+    vc[:, :, :, 0] = 1.0                                   # a column whose attention output must be 1
+    q = torch.randn(B, nh * d, device="cuda").bfloat16()
+    tables = torch.randperm(n_pages, device="cuda").to(torch.int32).view(B, -1)
+    ar = torch.arange(B, dtype=torch.int32, device="cuda")
+    ctxs = torch.tensor([ctx, ctx - 4097], dtype=torch.int32, device="cuda")
+    ref = torch.zeros(B, nh * d, dtype=torch.float32, device="cuda")
+    ops.attention_generic(q.float(), kc.float(), vc.float(), ref, ar, (ctxs - 1).contiguous(), tables, nh, nkv, d, ps, 0.125)
+    for splits in (ops.decode_splits(B, nkv, ctx), 2, 32):
+        out = torch.zeros_like(q)
+        scratch = torch.empty(B * nh * splits * (d + 2), dtype=torch.float32, device="cuda")
+        ops.attention_decode(q, kc, vc, out, ar, ar, ctxs, tables, nh, nkv, d, ps, 0.125, 0, splits, scratch)
+        assert (out.float() - ref).abs().max() <= 4e-3, splits
+        assert (out.float().view(B, nh, d)[:, :, 0] - 1.0).abs().max() <= 2 ** -7
+    ops.check_device_errors()
