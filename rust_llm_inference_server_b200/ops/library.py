@@ -72,6 +72,8 @@ def lib():
         handle.rlis_stream_gemm_set_target.restype = None
         handle.rlis_attention_decode_set_stages.argtypes = [c_int]
         handle.rlis_attention_decode_set_stages.restype = None
+        handle.rlis_sample_filtered_set_cluster.argtypes = [c_int]
+        handle.rlis_sample_filtered_set_cluster.restype = None
         handle.rlis_attention_decode_set_tma.argtypes = [c_int]
         handle.rlis_attention_decode_set_tma.restype = None
         handle.rlis_attention_decode_error.argtypes = []

@@ -449,6 +449,38 @@ def test_decode_attention_from_the_projection_equals_rotation_then_attention(geo
             assert not torch.equal(k2, dev(kc))                  # the newest keys did arrive
 
 
+@pytest.mark.parametrize("V", [1003, 4100, 50257, 128256, 200003])
+def test_filtered_sampling_cluster_and_one_cta_kernels_agree(V):
+    """The kernel that holds a row in the registers of a cluster picks the tokens of the kernel
+    that reads the row pass after pass (which the test before compares with the plain rule), at
+    vocabularies of every size class, with ties and with rows that a stride separates."""
+    from rust_llm_inference_server_b200 import ops
+    from rust_llm_inference_server_b200.ops.library import lib
+    rng = np.random.default_rng(V)
+    R = 12
+    logits = (rng.normal(size=(R, V + 3)) * 2.5).astype(np.float32)
+    logits[2, [7, V // 2, V - 1]] = logits[2, :V].max()
+    logits[3, :V] = 0.25
+    logits[4, 100:160] = np.sort(logits[4, :V])[-30]
+    settings = [(0.8, 0, 0.9), (1.0, 40, 1.0), (0.5, 10, 0.5), (1.4, 0, 0.3), (0.9, 1, 1.0), (1.0, V + 5, 0.95)]
+    params = np.zeros((R, 5), dtype=np.uint32)
+    for r in range(R):
+        T, k, p = settings[r % len(settings)]
+        u = int(rng.integers(0, 1 << 53, dtype=np.uint64))
+        params[r] = (np.float32(np.float32(1.0) / np.float32(T)).view(np.uint32), k, np.float32(p).view(np.uint32),
+                     u & 0xFFFFFFFF, u >> 32)
+    lt = torch.from_numpy(logits).cuda()[:, :V]                       # rows with a stride, not 16-byte aligned
+    pt = torch.from_numpy(params.view(np.int32)).cuda()
+    got = ops.sample_filtered(lt, pt).cpu().tolist()
+    lib().rlis_sample_filtered_set_cluster(0)
+    try:
+        want = ops.sample_filtered(lt, pt).cpu().tolist()
+    finally:
+        lib().rlis_sample_filtered_set_cluster(1)
+    assert got == want
+    assert got[3] < V and all(0 <= t < V for t in got)
+
+
 def test_sample_rows_equals_the_plain_sampler():
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(0)
