@@ -154,6 +154,7 @@ class LLMEngine:
         self._ids_dev = torch.zeros((n,), dtype=torch.int32, device=model.device)
         self._fids_dev = torch.zeros((n,), dtype=torch.int32, device=model.device)
         self._sampled = [torch.cuda.Event(), torch.cuda.Event()]
+        self._pen_host = self._pen_dev = None      # histories of the rows with a repetition penalty
         self._slot = 0
         self._inflight: _Launched | None = None
         # pages of a window group are handed out as a request grows, so a decode step can run out
@@ -219,6 +220,8 @@ class LLMEngine:
         for s in cur.rows:
             if s.id not in self.seqs or len(s.tokens) + 1 - s.prompt_len >= s.max_tokens:
                 return False
+            if s.sampler.params.repetition_penalty != 1.0:      # its history has to be complete on the host
+                return False
         return True
 
     def _launch(self, prev: _Launched | None) -> _Launched | None:
@@ -275,10 +278,11 @@ class LLMEngine:
     def _enqueue_sampler(self, L: _Launched) -> None:
         """Launches the samplers of a step's wanted rows and the copy of their ids to pinned
         memory.  Greedy and temperature rows: the device's Gumbel-max kernel; top-k / top-p rows:
-        the device's filtering kernel; rows with a repetition penalty: the host, when the ids are
-        read (crates/engine/src/engine.rs:643-708 has the same split, with all filtering on the
-        host)."""
+        the device's filtering kernel; a repetition penalty is applied to the logits on the device
+        before either (crates/engine/src/engine.rs:643-708 samples greedy and temperature rows on
+        the device and filters on the host)."""
         rows, n, k = L.rows, len(L.rows), L.slot
+        self._penalise(L)
         L.pos = [len(s.tokens) + (1 if L.ahead else 0) for s in rows]
         L.plain = [s.sampler.device_mode(p) for s, p in zip(rows, L.pos)]
         L.filt = [s.sampler.filtered_mode(p) if m is None else None for s, p, m in zip(rows, L.pos, L.plain)]
@@ -308,26 +312,46 @@ class LLMEngine:
         elif n_filt == n:
             L.ids_dev = self._fids_dev
 
+    def _penalise(self, L: _Launched) -> None:
+        """Repetition penalties, on the device and in place on the step's logits, before the sampling
+        kernels see them: the histories of the rows that have one go up in one copy.  (Such rows
+        are never launched ahead: their history is complete on the host.)"""
+        pen = [(i, s) for i, s in enumerate(L.rows) if s.sampler.params.repetition_penalty != 1.0]
+        if not pen:
+            return
+        total = sum(len(s.tokens) for _, s in pen)
+        n = len(pen)
+        need = total + 3 * n + 1
+        if self._pen_host is None or self._pen_host.numel() < need:
+            size = max(need, 2 * (self._pen_host.numel() if self._pen_host is not None else 4096))
+            self._pen_host = torch.zeros((size,), dtype=torch.int32, pin_memory=True)
+            self._pen_dev = torch.zeros((size,), dtype=torch.int32, device=self.model.device)
+        h = self._pen_host.numpy()
+        # layout: rows [n], offsets [n + 1], penalties [n] (float bits), then the tokens
+        o_off, o_pen, o_tok = n, 2 * n + 1, 3 * n + 1
+        at = 0
+        for j, (i, s) in enumerate(pen):
+            h[j] = i
+            h[o_off + j] = at
+            h[o_pen + j] = np.float32(s.sampler.params.repetition_penalty).view(np.int32)
+            h[o_tok + at:o_tok + at + len(s.tokens)] = s.tokens
+            at += len(s.tokens)
+        h[o_off + n] = at
+        d = self._pen_dev
+        d[:need].copy_(self._pen_host[:need], non_blocking=True)
+        ops.repetition_penalty(L.logits, d[:n], d[o_tok:o_tok + total], d[o_off:o_off + n + 1],
+                               d[o_pen:o_pen + n].view(torch.float32))
+        self.stats.h2d_bytes += need * 4
+
     def _collect(self, L: _Launched, nxt: _Launched | None):
         """Waits for a launched step's ids, records the tokens and finishes requests.  `nxt`: the
         step launched after it with placeholders, which now get their values."""
         new_tokens, finished = {}, []
         rows, n, k = L.rows, len(L.rows), L.slot
         if rows:
-            tokens = [0] * n
-            if any(m is not None for m in L.plain) or any(f is not None for f in L.filt):
-                self._sampled[k].synchronize()
-                a, b = self._ids_host[k][:n].tolist(), self._fids_host[k][:n].tolist()
-                for i in range(n):
-                    tokens[i] = a[i] if L.plain[i] is not None else b[i]
-            host_idx = [i for i in range(n) if L.plain[i] is None and L.filt[i] is None]
-            if host_idx:
-                sel = torch.tensor(host_idx, device=L.logits.device)
-                rows_host = L.logits.index_select(0, sel).to("cpu").numpy()
-                self.stats.d2h_bytes += rows_host.nbytes
-                for j, i in enumerate(host_idx):
-                    s = rows[i]
-                    tokens[i] = s.sampler.sample_host(rows_host[j], s.tokens, L.pos[i])
+            self._sampled[k].synchronize()
+            a, b = self._ids_host[k][:n].tolist(), self._fids_host[k][:n].tolist()
+            tokens = [a[i] if L.plain[i] is not None else b[i] for i in range(n)]
             now = time.perf_counter()
             for s, tok in zip(rows, tokens):
                 if s.id not in self.seqs:           # cancelled, or ended one step earlier (its row ran ahead)

@@ -450,6 +450,25 @@ def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | 
     return out
 
 
+def repetition_penalty(logits: torch.Tensor, rows: torch.Tensor, history: torch.Tensor, offsets: torch.Tensor,
+                       penalties: torch.Tensor) -> torch.Tensor:
+    """In place on float32 logits [R, V]: for row rows[i], every distinct token of
+    history[offsets[i]:offsets[i + 1]] has its logit divided by penalties[i] if positive, multiplied
+    otherwise (once, however often the token occurs)."""
+    R, V = logits.shape
+    n = rows.shape[0]
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise KernelError("repetition_penalty: logits must be float32 CUDA rows with unit stride")
+    _req(rows, "rows", torch.int32, (n,))
+    _req(history, "history", torch.int32, (None,))
+    _req(offsets, "offsets", torch.int32, (n + 1,))
+    _req(penalties, "penalties", torch.float32, (n,))
+    check(lib().rlis_repetition_penalty(logits.data_ptr(), rows.data_ptr(), history.data_ptr(), offsets.data_ptr(),
+                                        penalties.data_ptr(), n, V, logits.stride(0), _stream()), "repetition_penalty")
+    _count()
+    return logits
+
+
 def sample_filtered(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """One token id per row of float32 logits [R, V] by temperature sampling with top-k and/or
     top-p filtering on the device.  params int32 [R, 5] = (bits of 1/T, top_k (0: off), bits of

@@ -33,6 +33,7 @@ SIGNATURES = {
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
     "rlis_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_prefill_tc_takes": [I, I, I, I],
+    "rlis_repetition_penalty": [P, P, P, P, P, I, I, LL, P],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
     "rlis_sample_filtered": [P, P, P, I, I, LL, P],
     "rlis_nll_rows": [P, P, P, I, I, LL, P],

@@ -28,8 +28,8 @@ class SamplingParams:
     def is_greedy(self) -> bool:
         return self.temperature < 1e-5
 
-    def is_device_sampleable(self) -> bool:
-        """Greedy or temperature-only rows are picked by the kernel without the logits leaving
-        the GPU (sampler.rs:54-57); top-k, top-p and the penalty take the host path."""
-        return self.repetition_penalty == 1.0 and (
-            self.is_greedy() or (self.top_k == 0 and self.top_p >= 1.0))
+    def is_unfiltered(self) -> bool:
+        """Greedy or temperature-only rows: the Gumbel-max kernel picks them (sampler.rs:54-57);
+        rows with top-k or top-p go to the filtering kernel.  A repetition penalty is applied to
+        the logits on the device before either."""
+        return self.is_greedy() or (self.top_k == 0 and self.top_p >= 1.0)

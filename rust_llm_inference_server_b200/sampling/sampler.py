@@ -111,9 +111,9 @@ class Sampler:
 
     def device_mode(self, position: int):
         """(key, bits of 1/T) for the device's greedy / Gumbel-max sampler, or None when the row
-        needs filtering (see `filtered_mode`) or the host."""
+        needs filtering (see `filtered_mode`)."""
         p = self.params
-        if not p.is_device_sampleable():
+        if not p.is_unfiltered():
             return None
         if p.is_greedy():
             return (0, 0)
@@ -122,9 +122,9 @@ class Sampler:
 
     def filtered_mode(self, position: int):
         """(bits of 1/T, top_k, bits of top_p, low, high word of the uniform) for the device's
-        top-k / top-p sampler, or None (greedy, unfiltered, or a repetition penalty: host)."""
+        top-k / top-p sampler, or None (greedy or unfiltered rows)."""
         p = self.params
-        if p.repetition_penalty != 1.0 or p.is_greedy() or (p.top_k == 0 and p.top_p >= 1.0):
+        if p.is_unfiltered():
             return None
         inv_t = float(np.float32(1.0) / np.float32(p.temperature))
         u = unit_uniform_53(self.seed, position)

@@ -137,6 +137,23 @@ def test_seeded_sampling_is_reproducible_and_ignores_neighbours(model_root):
         lg = P.forward_logits(w, CONFIGS[which], toks)[-1].numpy()
         assert P.filtered_sample(lg, 0.9, 12, 0.85, P.uniform_53(11, len(toks))) == t
         toks.append(t)
+    # a repetition penalty changes the logits on the device before either sampler: greedy and filtered
+    # rows with a penalty, in one batch with a row that has none, replayed with the plain rules
+    sps = [SamplingParams(max_tokens=10, repetition_penalty=1.8),
+           SamplingParams(max_tokens=10, temperature=0.9, top_k=12, top_p=0.85, repetition_penalty=1.5, seed=11),
+           SamplingParams(max_tokens=10)]
+    outs = llm.generate(prompts[:3], sps)
+    assert outs[2].token_ids == llm.generate([prompts[2]], sps[2])[0].token_ids
+    assert outs[0].token_ids != llm.generate([prompts[0]], sps[2])[0].token_ids      # the penalty shows
+    for p, sp, o in zip(prompts[:2], sps[:2], outs[:2]):
+        toks = list(p)
+        for t in o.token_ids:
+            lg = P.forward_logits(w, CONFIGS[which], toks)[-1].numpy()
+            lg = P.apply_repetition_penalty(lg, toks, sp.repetition_penalty)
+            want = int(np.argmax(lg)) if sp.temperature == 0 else \
+                P.filtered_sample(lg, sp.temperature, sp.top_k, sp.top_p, P.uniform_53(sp.seed, len(toks)))
+            assert want == t
+            toks.append(t)
 
 
 def test_end_of_sequence_and_limits(model_root, tmp_path):

@@ -481,6 +481,36 @@ def test_filtered_sampling_cluster_and_one_cta_kernels_agree(V):
     assert got[3] < V and all(0 <= t < V for t in got)
 
 
+@pytest.mark.parametrize("V", [1003, 128256])
+def test_repetition_penalty_on_the_device_equals_the_plain_rule(V):
+    """Rows with a stride, histories with repeated tokens (penalised once), positive and negative
+    logits, an exact zero, an empty history, and a row that is not in the list and must stay."""
+    from rust_llm_inference_server_b200 import ops
+    rng = np.random.default_rng(V)
+    R = 5
+    logits = rng.normal(size=(R, V)).astype(np.float32) * 4
+    logits[1, 7] = 0.0
+    hist = {0: rng.integers(0, V, size=900).tolist() + [3] * 40, 1: [7, 7, 7, V - 1, 0, V - 1], 3: [],
+            4: rng.integers(0, 50, size=3000).tolist()}          # row 4: every token many times
+    pens = {0: 1.3, 1: 2.0, 3: 1.7, 4: 0.8}
+    order = [4, 0, 3, 1]                                          # the list names rows in any order
+    flat, offs = [], [0]
+    for r in order:
+        flat += hist[r]
+        offs.append(len(flat))
+    big = np.concatenate([logits, np.full((R, 3), 9.0, np.float32)], axis=1)
+    lt = torch.from_numpy(big).cuda()[:, :V]
+    ops.repetition_penalty(lt, torch.tensor(order, dtype=torch.int32).cuda(),
+                           torch.tensor(flat + [0], dtype=torch.int32).cuda()[:len(flat)],
+                           torch.tensor(offs, dtype=torch.int32).cuda(),
+                           torch.tensor([pens[r] for r in order], dtype=torch.float32).cuda())
+    got = lt.cpu().numpy()
+    for r in range(R):
+        want = P.apply_repetition_penalty(logits[r], hist[r], pens[r]) if r in hist else logits[r]
+        assert np.array_equal(got[r], want), r
+    assert not np.array_equal(got[0], logits[0]) and np.array_equal(got[2], logits[2])
+
+
 def test_sample_rows_equals_the_plain_sampler():
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(0)

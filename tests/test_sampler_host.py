@@ -23,7 +23,9 @@ def test_modes():
     assert k == P.row_key(9, 5) and bits == int(np.float32(2.0).view(np.uint32))
     assert Sampler(SamplingParams(temperature=0.5, top_p=0.9)).device_mode(0) is None
     assert Sampler(SamplingParams(temperature=0.5, top_k=3)).device_mode(0) is None
-    assert Sampler(SamplingParams(repetition_penalty=1.1)).device_mode(0) is None
+    # a repetition penalty changes the logits on the device first, not the way of drawing
+    assert Sampler(SamplingParams(repetition_penalty=1.1)).device_mode(0) == (0, 0)
+    assert Sampler(SamplingParams(temperature=0.5, top_k=3, repetition_penalty=1.1)).filtered_mode(0) is not None
     assert Sampler(SamplingParams(top_p=0.5)).device_mode(0) == (0, 0)   # greedy ignores filters
 
 
