@@ -36,6 +36,17 @@
 // Epilogues: bf16 or float32 y, or SwiGLU on a gate|up matrix whose rows are interleaved in blocks
 // of 4 (rows 8t..8t+3 gate, 8t+4..8t+7 up): y[m, 4t + j] = silu(gate_j) * up_j.
 //
+// The RMSNorm between two products of a decode step costs a kernel of its own although it moves a
+// few kilobytes.  Two more epilogues take it apart and into the products on either side (the
+// product is linear in x, so the norm's scale of a row may be applied after it):
+//   * "sink" (the last product of a mixer or feed-forward): the finisher adds its result, rounded
+//     to bf16 as the unfused path rounds it, to the float32 residual stream in place, writes
+//     xn = bf16(resid * norm_weight) for the product that follows, and the sum of resid^2 over
+//     its 128 features of every token into partials[tile][token] (a fixed tree over the CTA);
+//   * "scaled rows" (the first product of the next part): x is such an xn; the finisher multiplies
+//     its sums by 1 / sqrt(sum of the token's partials in the order of the tiles / dim + eps).
+// Both are deterministic and depend on the token's own values only.
+//
 // Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets an error word
 // (rlis_stream_gemm_error), every role runs to its end without further waits, and the CTA frees
 // its tensor memory before it returns.
@@ -52,7 +63,7 @@ constexpr int S_THREADS = 128;
 constexpr int MAX_SPLITS = 16;          // the largest cluster (above 8 is opt-in)
 
 template <int NT> constexpr size_t stream_smem_bytes() {
-    return (size_t)S_STAGES * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 128;
+    return (size_t)S_STAGES * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
 }
 
 struct SCtrl {
@@ -62,6 +73,20 @@ struct SCtrl {
     uint64_t red_full;      // the partial sums of the tokens this CTA finishes have arrived from the cluster
     uint32_t tmem_base;
     int abort;
+    float red[4];           // sink epilogue: the warps' sums of squares
+    float rstd[128];        // scaled rows: the norm's scale of every token
+};
+
+// What the two norm epilogues need (all null / 0 when unused).
+struct NormFuse {
+    const float* in_partials;   // [n_partials, M]: sums of squares of the rows x was made from
+    int n_partials;
+    int dim;                    // the norm's width
+    float eps;
+    float* resid;               // sink: [M, N] float32, updated in place
+    const float* norm_w;        // sink: [N] weight of the norm that follows
+    bf16* xn;                   // sink: [M, N] = bf16(resid * norm_w)
+    float* out_partials;        // sink: [tiles, M]
 };
 
 // A float into the shared memory of the cluster's CTA `rank` (at the offset of `local`), counted
@@ -86,11 +111,29 @@ __device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t
     }
 }
 
+// Sink epilogue for token t, called by all threads of the CTA together (it holds two barriers):
+// the thread's feature f of resid += bf16(v); xn = bf16(resid * w); the CTA's sum of resid^2 to
+// partials[tile][t].  `live` false: the barriers only.
+__device__ __forceinline__ void sink_token(const NormFuse& nf, float* red, float v, int t, int f, int tile, int M,
+                                           int N, bool live, float r_old, float w) {
+    float r = 0.f;
+    if (live && f < N) {
+        r = r_old + __bfloat162float(__float2bfloat16_rn(v));
+        nf.resid[(size_t)t * N + f] = r;
+        nf.xn[(size_t)t * N + f] = __float2bfloat16_rn(r * w);
+    }
+    const float s = warp_sum(r * r);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0 && live) nf.out_partials[(size_t)tile * M + t] = (red[0] + red[1]) + (red[2] + red[3]);
+    __syncthreads();
+}
+
 template <int NT, int EPI, typename OutT>
 __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 OutT* __restrict__ y, int M, int N, int K,
-                                                                int kb_per_split) {
+                                                                int kb_per_split, const NormFuse nf) {
     extern __shared__ unsigned char sg_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sg_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int X_STAGE_BYTES = NT * SK * 2;
@@ -171,12 +214,26 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     }
     __syncwarp();
     pdl_wait();            // nothing is stored before the kernels before this one have finished
+    const bool scaled = EPI != 2 && nf.in_partials != nullptr;
+    if (scaled && (int)threadIdx.x < M) {
+        // this token's scale: the partial sums in the order of the tiles (RMSNorm: 1 / sqrt(mean + eps))
+        float ss = 0.f;
+        for (int p = 0; p < nf.n_partials; ++p) ss += nf.in_partials[(size_t)p * M + threadIdx.x];
+        ctrl->rstd[threadIdx.x] = 1.0f / sqrtf(ss / (float)nf.dim + nf.eps);
+    }
+    // sink: what the first token this thread finishes needs from memory, requested before the sums arrive
+    const int f = n0 + warp * 32 + lane;
+    float sink_w = 0.f, sink_r0 = 0.f;
+    if (EPI == 2 && f < N) {
+        sink_w = nf.norm_w[f];
+        const int t0 = splits == 1 ? 0 : split;
+        if (t0 < M) sink_r0 = nf.resid[(size_t)t0 * N + f];
+    }
     const bool waited = has_work ? bar_wait(&ctrl->acc_full, 0, &ctrl->abort) : true;
     const bool ok = __syncthreads_and(waited ? 1 : 0) != 0;       // the same for all threads
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // epilogue: warp w reads TMEM lanes 32 w .. 32 w + 31; lane = feature, column = token
-    const int f = n0 + warp * 32 + lane;
     const uint32_t tmem_acc = tmem_base + ((uint32_t)(warp * 32) << 16);
     if (splits == 1) {
 #pragma unroll 1
@@ -184,10 +241,22 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
             if (c * 16 >= M) break;
             uint32_t r[16];
             tmem_ld16(tmem_acc + (uint32_t)(c * 16), r);
+            if (EPI == 2) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int t = c * 16 + j;
+                    if (t >= M) continue;           // the same for all threads
+                    const float r_old = t == 0 ? sink_r0 : (ok && f < N ? nf.resid[(size_t)t * N + f] : 0.f);
+                    sink_token(nf, ctrl->red, __uint_as_float(r[j]), t, f, tile, M, N, ok, r_old, sink_w);
+                }
+                continue;
+            }
             if (!ok) continue;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                if (c * 16 + j < M) store_token<EPI, OutT>(y, __uint_as_float(r[j]), c * 16 + j, f, lane, N);
+                if (c * 16 + j < M)
+                    store_token<EPI, OutT>(y, __uint_as_float(r[j]) * (scaled ? ctrl->rstd[c * 16 + j] : 1.0f),
+                                           c * 16 + j, f, lane, N);
         }
     } else {
         // Once every CTA of the cluster is done with its products, the stages are free everywhere:
@@ -217,11 +286,17 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         }
         if (split < M) {
             const bool got = bar_wait(&ctrl->red_full, 0, &ctrl->abort);
+            const bool good = EPI == 2 ? __syncthreads_and(ok && got ? 1 : 0) != 0 : (ok && got);
 #pragma unroll 1
             for (int t = split, slot = 0; t < M; t += splits, ++slot) {
                 float v = 0.f;
                 for (int s = 0; s < splits; ++s) v += part[(slot * splits + s) * SF + (int)threadIdx.x];
-                if (ok && got) store_token<EPI, OutT>(y, v, t, f, lane, N);
+                if (EPI == 2) {
+                    const float r_old = slot == 0 ? sink_r0 : (good && f < N ? nf.resid[(size_t)t * N + f] : 0.f);
+                    sink_token(nf, ctrl->red, v, t, f, tile, M, N, good, r_old, sink_w);
+                } else if (good) {
+                    store_token<EPI, OutT>(y, v * (scaled ? ctrl->rstd[t] : 1.0f), t, f, lane, N);
+                }
             }
         }
     }
@@ -236,7 +311,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
 int g_target_ctas = 0;      // 0: 1.3 times the number of SMs
 
 template <int NT, int EPI, typename OutT>
-int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, cudaStream_t stream) {
+int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, const NormFuse& nf, cudaStream_t stream) {
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, W, N, K, SF) || !make_map(&map_x, x, M, K, NT)) return RLIS_ERR_UNSUPPORTED;
     static bool attr_done = false;
@@ -260,16 +335,16 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, cu
     const int per = (k_blocks + splits - 1) / splits;
     rlis_launch_cluster(stream_gemm_kernel<NT, EPI, OutT>, dim3((unsigned)tiles, (unsigned)splits), S_THREADS,
                         stream_smem_bytes<NT>(), stream, dim3(1, (unsigned)splits, 1), map_w, map_x, (OutT*)y, M, N, K,
-                        per);
+                        per, nf);
     return RLIS_LAUNCH_CHECK();
 }
 
 template <int NT>
 int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, int out_dtype, int epilogue,
-                    cudaStream_t stream) {
-    if (epilogue == 0 && out_dtype == RLIS_BF16) return launch_stream<NT, 0, bf16>(x, W, y, M, N, K, stream);
-    if (epilogue == 0 && out_dtype == RLIS_F32) return launch_stream<NT, 0, float>(x, W, y, M, N, K, stream);
-    if (epilogue == 1 && out_dtype == RLIS_BF16) return launch_stream<NT, 1, bf16>(x, W, y, M, N, K, stream);
+                    const NormFuse& nf, cudaStream_t stream) {
+    if (epilogue == 0 && out_dtype == RLIS_BF16) return launch_stream<NT, 0, bf16>(x, W, y, M, N, K, nf, stream);
+    if (epilogue == 0 && out_dtype == RLIS_F32) return launch_stream<NT, 0, float>(x, W, y, M, N, K, nf, stream);
+    if (epilogue == 1 && out_dtype == RLIS_BF16) return launch_stream<NT, 1, bf16>(x, W, y, M, N, K, nf, stream);
     return RLIS_ERR_UNSUPPORTED;
 }
 }  // namespace
@@ -282,15 +357,47 @@ extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }
 // out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (SwiGLU, rows of W interleaved
 // gate/up in blocks of 4, N a multiple of 8): y [M, N / 2].  M up to 128; K a multiple of 8;
 // x and W 16-byte aligned.
-extern "C" int rlis_stream_gemm_bf16(const void* x, const void* W, void* y, int M, int N, int K,
-                                     int out_dtype, int epilogue, cudaStream_t stream) {
+//
+// Scaled rows (epilogues 0 and 1; in_partials not null): x is bf16(resid * norm weight) and
+// in_partials [n_partials, M] the sums of squares that a sink product left; y is multiplied by
+// 1 / sqrt(sum / norm_dim + eps) of its row.
+// Sink (epilogue 2, M up to 16; y unused): resid [M, N] float32 += bf16(x W^T) in place,
+// xn [M, N] bf16 = resid * norm_w, out_partials [ceil(N / 128), M] = sums of resid^2 by 128 features.
+extern "C" int rlis_stream_gemm_fused(const void* x, const void* W, void* y, int M, int N, int K, int out_dtype,
+                                      int epilogue, const float* in_partials, int n_partials, int norm_dim, float eps,
+                                      float* resid, const float* norm_w, void* xn, float* out_partials,
+                                      cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K <= 0 || (K & 7) != 0) return RLIS_ERR_UNSUPPORTED;
     if (epilogue == 1 && (N & 7) != 0) return RLIS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
-    if (M <= 16) return dispatch_stream<16>(x, W, y, M, N, K, out_dtype, epilogue, stream);
-    if (M <= 32) return dispatch_stream<32>(x, W, y, M, N, K, out_dtype, epilogue, stream);
-    if (M <= 64) return dispatch_stream<64>(x, W, y, M, N, K, out_dtype, epilogue, stream);
-    return dispatch_stream<128>(x, W, y, M, N, K, out_dtype, epilogue, stream);
+    NormFuse nf{};
+    if (in_partials != nullptr) {
+        if (epilogue == 2 || n_partials <= 0 || norm_dim <= 0) return RLIS_ERR_UNSUPPORTED;
+        nf.in_partials = in_partials;
+        nf.n_partials = n_partials;
+        nf.dim = norm_dim;
+        nf.eps = eps;
+    }
+    if (epilogue == 2) {
+        if (M > 16 || resid == nullptr || norm_w == nullptr || xn == nullptr || out_partials == nullptr)
+            return RLIS_ERR_UNSUPPORTED;
+        nf.resid = resid;
+        nf.norm_w = norm_w;
+        nf.xn = reinterpret_cast<bf16*>(xn);
+        nf.out_partials = out_partials;
+        return launch_stream<16, 2, bf16>(x, W, nullptr, M, N, K, nf, stream);
+    }
+    if (M <= 16) return dispatch_stream<16>(x, W, y, M, N, K, out_dtype, epilogue, nf, stream);
+    if (M <= 32) return dispatch_stream<32>(x, W, y, M, N, K, out_dtype, epilogue, nf, stream);
+    if (M <= 64) return dispatch_stream<64>(x, W, y, M, N, K, out_dtype, epilogue, nf, stream);
+    return dispatch_stream<128>(x, W, y, M, N, K, out_dtype, epilogue, nf, stream);
+}
+
+extern "C" int rlis_stream_gemm_bf16(const void* x, const void* W, void* y, int M, int N, int K,
+                                     int out_dtype, int epilogue, cudaStream_t stream) {
+    if (epilogue == 2) return RLIS_ERR_UNSUPPORTED;
+    return rlis_stream_gemm_fused(x, W, y, M, N, K, out_dtype, epilogue, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr,
+                                  nullptr, stream);
 }

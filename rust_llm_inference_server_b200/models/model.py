@@ -118,7 +118,13 @@ class Model:
         delta = None
         for ci, call in enumerate(self.calls):
             blk = self.blocks[call.layer]
-            resid, delta = blk.forward(resid, delta, step, caches[call.cache], states[ci], call.writes_cache)
+            nxt = self.blocks[self.calls[ci + 1].layer] if ci + 1 < len(self.calls) else None
+            if getattr(blk, "chains_norms", False) and hasattr(nxt, "entry_sink"):
+                # the block may leave its last addition and the next block's first norm to the products around them
+                resid, delta = blk.forward(resid, delta, step, caches[call.cache], states[ci], call.writes_cache,
+                                           next_block=nxt)
+            else:
+                resid, delta = blk.forward(resid, delta, step, caches[call.cache], states[ci], call.writes_cache)
         return resid, delta
 
     def logits(self, resid, delta, step, rows: torch.Tensor):

@@ -11,6 +11,7 @@ no reduced-precision matrix mode can enter.
 from __future__ import annotations
 
 import functools
+import os
 
 import torch
 
@@ -132,25 +133,83 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+FUSE_NORMS = os.environ.get("RLIS_FUSE_NORMS", "1") != "0"     # for measurements: 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
 DECODE_GEMM_ROWS = 16     # up to this many rows `linear` uses it; longer batches go to the library GEMM
 
 
-def stream_gemm(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False) -> torch.Tensor:
+class ScaledRows:
+    """Rows of a norm's output whose scale is still to be applied: `x` = bf16(resid * weight) [T, dim]
+    and `partials` float32 [P, T], the sums of resid^2 over P slices of the width.  The product that
+    takes them multiplies its result by 1 / sqrt(sum of a row's partials / dim + eps): the norm
+    between two decode products without a kernel of its own.  Made by `stream_gemm(..., sink=)`."""
+
+    def __init__(self, x, partials, dim, eps):
+        self.x, self.partials, self.dim, self.eps = x, partials, int(dim), float(eps)
+
+    shape = property(lambda self: self.x.shape)
+    dtype = property(lambda self: self.x.dtype)
+    device = property(lambda self: self.x.device)
+
+
+class ResidualSink:
+    """Where the last product of a part may put its result itself: added to the float32 residual
+    stream `resid` [T, dim] in place, and handed on as the ScaledRows of the RMSNorm that follows
+    (`weight` float32 [dim], `eps`)."""
+
+    def __init__(self, resid, weight, eps):
+        self.resid, self.weight, self.eps = resid, weight, float(eps)
+
+
+def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = False, sink: ResidualSink | None = None):
     """y = x @ w^T for at most 128 rows of bfloat16 x: the decode step's weight-streaming product on
     the tcgen05 tensor cores (TMA-fed, weights as the M side, k split over CTAs).  `swiglu4`: w is a
-    gate|up matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, [M, N / 2]."""
+    gate|up matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, [M, N / 2].
+    `x` may be ScaledRows: the rows' scale is applied to the result.  `sink` (up to 16 rows): the
+    result, rounded to bfloat16, is added to sink.resid in place and the ScaledRows of the norm that
+    follows are returned instead of y."""
+    scaled = x if isinstance(x, ScaledRows) else None
+    if scaled is not None:
+        x = scaled.x
     M, K = x.shape
     N = w.shape[0]
     _req(x, "x", torch.bfloat16)
     _req(w, "w", torch.bfloat16, (N, K))
     if M > STREAM_MAX_ROWS or K % 8 or (swiglu4 and N % 8):
         raise KernelError(f"stream_gemm: takes up to {STREAM_MAX_ROWS} rows and K a multiple of 8, got M={M}, K={K}")
-    out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
-    check(lib().rlis_stream_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
-                                      1 if swiglu4 else 0, _stream()), "stream_gemm")
+    if scaled is None and sink is None:
+        out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
+        check(lib().rlis_stream_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
+                                          1 if swiglu4 else 0, _stream()), "stream_gemm")
+        _count()
+        return out
+    in_p, n_p, dim, eps = 0, 0, 0, 0.0
+    if scaled is not None:
+        if sink is not None:
+            raise KernelError("stream_gemm: scaled rows into a sink are not supported")
+        n_p = scaled.partials.shape[0]
+        _req(scaled.partials, "partials", torch.float32, (n_p, M))
+        if scaled.dim != K:
+            raise KernelError(f"stream_gemm: scaled rows of width {scaled.dim} for a product over {K}")
+        in_p, dim, eps = scaled.partials.data_ptr(), scaled.dim, scaled.eps
+    if sink is None:
+        out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
+        check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
+                                           1 if swiglu4 else 0, in_p, n_p, dim, eps, 0, 0, 0, 0, _stream()),
+              "stream_gemm")
+        _count()
+        return out
+    if swiglu4 or M > DECODE_GEMM_ROWS:
+        raise KernelError(f"stream_gemm: a sink takes a plain product of up to {DECODE_GEMM_ROWS} rows")
+    _req(sink.resid, "sink.resid", torch.float32, (M, N))
+    _req(sink.weight, "sink.weight", torch.float32, (N,))
+    xn = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    partials = torch.empty(((N + 127) // 128, M), dtype=torch.float32, device=x.device)
+    check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), 0, M, N, K, _code(torch.bfloat16), 2, 0, 0, 0, 0.0,
+                                       sink.resid.data_ptr(), sink.weight.data_ptr(), xn.data_ptr(),
+                                       partials.data_ptr(), _stream()), "stream_gemm")
     _count()
-    return out
+    return ScaledRows(xn, partials, N, sink.eps)
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> torch.Tensor:
@@ -182,10 +241,22 @@ def check_device_errors() -> None:
         raise KernelError(f"a bounded mbarrier wait of a tcgen05 kernel ran out on the device (code {code})")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
+def fuses_norms(n_rows: int, dtype, *widths: int) -> bool:
+    """Whether products over `widths` of a step of `n_rows` rows go to the kernel that takes
+    ScaledRows and a ResidualSink."""
+    return (FUSE_NORMS and dtype == torch.bfloat16 and 0 < n_rows <= DECODE_GEMM_ROWS
+            and all(w % 8 == 0 for w in widths))
+
+
+def linear(x, w: torch.Tensor, out_dtype=None, sink: ResidualSink | None = None):
     """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
     16 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
-    accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits)."""
+    accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits).
+    ScaledRows as x and a `sink` are for the streaming kernel only (see `fuses_norms`)."""
+    if isinstance(x, ScaledRows) or sink is not None:
+        if not fuses_norms(x.shape[0], x.dtype, x.shape[1]):
+            raise KernelError("linear: scaled rows or a sink with a product that does not take them")
+        return stream_gemm(x, w, out_dtype or torch.bfloat16, sink=sink)
     if x.dtype == torch.float32:
         return gemm_f32(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:

@@ -39,6 +39,7 @@ SIGNATURES = {
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
     "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
+    "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, P],
 }
 
 OPTIONAL_SIGNATURES: dict = {}

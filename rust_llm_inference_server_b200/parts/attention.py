@@ -55,7 +55,11 @@ class GQAAttention(Mixer):
         s = self.spec
         return ops.decode_splits(step.n_decode, s.n_kv_heads, step.max_decode_ctx) if step.n_decode else None
 
-    def forward(self, x, step, cache, state, writes_cache=True):
+    def fuses_norms(self, step) -> bool:
+        s = self.spec
+        return ops.fuses_norms(step.n_tokens, self.dtype, s.hidden, s.n_heads * s.head_dim)
+
+    def forward(self, x, step, cache, state, writes_cache=True, sink=None):
         s = self.spec
         T = x.shape[0]
         qkv = ops.linear(x, self.w_qkv)
@@ -68,13 +72,13 @@ class GQAAttention(Mixer):
                 ops.attention_decode_from_qkv(qkv, cache.k, cache.v, o, step, cache.group, table, writes_cache,
                                               s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size,
                                               self.scale, self.window)
-                return ops.linear(o, self.w_o)
+                return ops.linear(o, self.w_o, sink=sink)
         q = step.buffer("attn_q", (T, s.n_heads * s.head_dim), self.dtype)
         self.position.encode_and_store(qkv, q, cache, step, s.n_heads, s.n_kv_heads, s.head_dim,
                                        store=writes_cache)
         ops.attention(q, cache.k, cache.v, o, step, cache.group, s.n_heads, s.n_kv_heads,
                       s.head_dim, cache.page_size, self.scale, self.window)
-        return ops.linear(o, self.w_o)
+        return ops.linear(o, self.w_o, sink=sink)
 
 
 register_mixer("gqa_attention", GQAAttention)

@@ -35,6 +35,14 @@ class Part:
         with equal variants replay the same captured graph."""
         return None
 
+    def fuses_norms(self, step) -> bool:
+        """Mixers and feed-forwards: True when, in this step, `forward` takes `ops.ScaledRows` for x
+        (rows of the norm before it whose scale its first product applies) and a keyword `sink`
+        (an `ops.ResidualSink`: its last product adds the result to the residual stream itself and
+        returns the ScaledRows of the norm that follows instead of its output).  The arrangement
+        asks before it passes either; a part that says nothing gets and returns plain tensors."""
+        return False
+
     def tensors(self) -> dict:
         """Checkpoint tensors this part reads: {name: shape}."""
         return {}
@@ -98,6 +106,12 @@ class Norm(Part):
     def forward_rows(self, resid, delta, step, rows: torch.Tensor) -> torch.Tensor:
         """The same for the rows `rows` only (the places whose logits are wanted)."""
         return self.forward(resid, delta, step).index_select(0, rows.long())
+
+    def sink(self, resid: torch.Tensor, step):
+        """An `ops.ResidualSink` for this norm over `resid` when, in this step, the product before
+        it may do the addition and the product after it the scaling (see `Part.fuses_norms`), or
+        None (the default): the norm then runs as a kernel of its own."""
+        return None
 
 
 class PositionEncoding(Part):

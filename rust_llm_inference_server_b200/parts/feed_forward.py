@@ -37,7 +37,10 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         self.w_down = src.get(s.down_proj).contiguous()
 
-    def forward(self, x, step):
+    def fuses_norms(self, step) -> bool:
+        return ops.fuses_norms(step.n_tokens, self.dtype, self.spec.hidden, self.spec.intermediate)
+
+    def forward(self, x, step, sink=None):
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
         if fusable and x.shape[0] <= ops.DECODE_GEMM_ROWS:
             act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
@@ -49,7 +52,7 @@ class SwiGLU(FeedForward):
             gu = ops.linear(x, self.w_gate_up)
             act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
             ops.swiglu(gu, act, self.interleave)
-        return ops.linear(act, self.w_down)
+        return ops.linear(act, self.w_down, sink=sink)
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -36,5 +36,10 @@ class RMSNorm(Norm):
         out = step.buffer("norm_rows_out", (rows.shape[0], self.dim), self.dtype)
         return ops.rmsnorm(resid, self.weight, self.eps, out, delta, rows)
 
+    def sink(self, resid, step):
+        if not ops.fuses_norms(resid.shape[0], self.dtype, self.dim):
+            return None
+        return ops.ResidualSink(resid, self.weight, self.eps)
+
 
 register_norm("rmsnorm", RMSNorm)

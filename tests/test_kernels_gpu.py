@@ -109,6 +109,56 @@ def test_streaming_product_for_decode_rows(shape):
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (8, 2048, 8192), (16, 520, 264), (5, 1000, 4104), (3, 128, 64)])
+def test_streaming_product_takes_a_norm_apart(M, N, K):
+    """The norm between two decode products without a kernel of its own: the first product adds
+    its result to the residual stream and leaves bf16(resid * weight) and sums of squares by 128
+    features (one CTA, and clusters that split k; widths that are no multiple of 128), the second
+    multiplies by the row's scale.  Against the plain formulas, and against itself run twice."""
+    from rust_llm_inference_server_b200 import ops
+    torch.manual_seed(N + K)
+    x, w = torch.randn(M, K).bfloat16(), (torch.randn(N, K) * 0.05).bfloat16()
+    resid0, nw, eps = torch.randn(M, N) * 2, torch.rand(N) + 0.5, 1e-5
+    resid0[0, 3 % N] = 300.0                                  # one feature that carries most of a row's square
+    resid = dev(resid0.clone())
+    rows = ops.stream_gemm(dev(x), dev(w), sink=ops.ResidualSink(resid, dev(nw), eps))
+    delta = x.double() @ w.double().t()
+    new = resid.cpu()
+    assert bool(((new.double() - resid0.double() - delta).abs() <= 2.0 ** -8 * delta.abs() + 1e-4).all())
+    assert torch.equal(rows.x.cpu(), (new * nw).bfloat16())                   # from the sums it stored, exactly
+    P_ = (N + 127) // 128
+    assert rows.partials.shape == (P_, M) and rows.dim == N
+    sq = torch.zeros(P_ * 128, M, dtype=torch.float64)
+    sq[:N] = new.double().t() ** 2
+    want_p = sq.view(P_, 128, M).sum(1)
+    assert bool(((rows.partials.cpu().double() - want_p).abs() <= 1e-6 * want_p + 1e-12).all())
+    resid2 = dev(resid0.clone())
+    again = ops.stream_gemm(dev(x), dev(w), sink=ops.ResidualSink(resid2, dev(nw), eps))
+    assert torch.equal(resid2, resid) and torch.equal(again.partials, rows.partials)      # no race in the sums
+    one = dev(resid0[M // 2:M // 2 + 1].clone())
+    r1 = ops.stream_gemm(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w), sink=ops.ResidualSink(one, dev(nw), eps))
+    assert torch.equal(one[0], resid[M // 2]) and torch.equal(r1.partials[:, 0], rows.partials[:, M // 2])   # a row ignores its neighbours
+
+    # the second product: plain, float32 and gated epilogues apply the scale
+    I = 264
+    w2 = (torch.randn(2 * I, N) * 0.05).bfloat16()
+    rstd = 1.0 / torch.sqrt((new.double() ** 2).mean(1) + eps)
+    want = (rows.x.cpu().double() @ w2.double().t()) * rstd[:, None]
+    got32 = ops.stream_gemm(rows, dev(w2), torch.float32).cpu()
+    assert bool(((got32.double() - want).abs() <= 1e-5 * want.abs() + 2e-5 * math.sqrt(N)).all())
+    got16 = ops.linear(rows, dev(w2)).cpu()
+    assert bool(((got16.double() - want).abs() <= 2.0 ** -8 * want.abs() + 1e-4).all())
+    gated = ops.stream_gemm(rows, dev(w2), swiglu4=True).cpu()
+    g, u = want.view(M, -1, 2, 4)[:, :, 0].reshape(M, I), want.view(M, -1, 2, 4)[:, :, 1].reshape(M, I)
+    wg = torch.nn.functional.silu(g) * u
+    assert bool(((gated.double() - wg).abs() <= 2.0 ** -7 * wg.abs() + 1e-3).all())
+    # and the whole against the norm as a kernel of its own followed by the product (two roundings apart)
+    normed = P.rms_norm(new, nw, eps).bfloat16()
+    ref = normed.double() @ w2.double().t()
+    assert bool(((got32.double() - ref).abs() <= 2.0 ** -7 * ref.abs() + 2.0 ** -8 * ref.abs().max()).all())
+    ops.check_device_errors()
+
+
 def test_streaming_product_refuses_what_it_cannot_take():
     from rust_llm_inference_server_b200 import ops
     from rust_llm_inference_server_b200.ops.library import KernelError
