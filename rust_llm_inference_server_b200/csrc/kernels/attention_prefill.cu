@@ -41,8 +41,9 @@ __global__ __launch_bounds__(PF_THREADS) void attn_prefill_mma_kernel(
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
-    const int b = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
-    const int head = blockIdx.y;
+    // x: the head, y: the tile; CTAs start in the order of the tile list across all heads
+    const int b = tiles[2 * blockIdx.y], t0 = tiles[2 * blockIdx.y + 1];
+    const int head = blockIdx.x;
     const int kvh = head / (nh / nkv);
     const int q_start = cu_seqlens[b];
     const int q_len = cu_seqlens[b + 1] - q_start;
@@ -244,9 +245,9 @@ extern "C" int rlis_attention_prefill(const void* q, const void* k_cache, const 
                                       int d, int page_size, float scale, int window, int dtype,
                                       cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (dtype != RLIS_BF16 || (d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || nh > 65535)
+    if (dtype != RLIS_BF16 || (d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || n_tiles > 65535)
         return RLIS_ERR_UNSUPPORTED;
-    dim3 grid(n_tiles, nh);
+    dim3 grid(nh, n_tiles);
     static bool attr_done = false;
     if (!attr_done) {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -129,8 +129,9 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nrep = nh / nkv;
-    const int b = tiles[2 * blockIdx.x], t0 = tiles[2 * blockIdx.x + 1];
-    const int head0 = blockIdx.y * 2;
+    // x: the pair of heads, y: the tile; CTAs start in the order of the tile list across all heads
+    const int b = tiles[2 * blockIdx.y], t0 = tiles[2 * blockIdx.y + 1];
+    const int head0 = blockIdx.x * 2;
     const int kvh = head0 / nrep;
     const int q_start = cu_seqlens[b];
     const int q_len = cu_seqlens[b + 1] - q_start;
@@ -391,7 +392,7 @@ extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, con
                                          int n_tokens, int n_pages, int nh, int nkv, int d, int page_size,
                                          float scale, int window, int dtype, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (dtype != RLIS_BF16 || !rlis_attention_prefill_tc_takes(nh, nkv, d, page_size) || nh / 2 > 65535)
+    if (dtype != RLIS_BF16 || !rlis_attention_prefill_tc_takes(nh, nkv, d, page_size) || n_tiles > 65535)
         return RLIS_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
           reinterpret_cast<uintptr_t>(out)) & 15) != 0)
@@ -408,7 +409,7 @@ extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, con
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM);
         attr_done = true;
     }
-    rlis_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles, (unsigned)(nh / 2)), PT_THREADS, PT_SMEM, stream,
+    rlis_launch(attn_prefill_tc_kernel, dim3((unsigned)(nh / 2), (unsigned)n_tiles), PT_THREADS, PT_SMEM, stream,
                 map_q, map_k, map_v, (bf16*)out, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv,
                 page_size, (int)cache_rows, scale, window);
     return RLIS_LAUNCH_CHECK();

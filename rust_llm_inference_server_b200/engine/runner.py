@@ -187,6 +187,9 @@ class ModelRunner:
             k += n
         Bd, Tp = len(dec_rows), len(pf_rows)
         pf_tiles = [(b, t0) for b, n in enumerate(lens) if n > 1 for t0 in range(0, n, self.PREFILL_TILE)]
+        # the tiles with the most keys to read first: the GPU hands out CTAs in this order, and the
+        # long ones must not be the last to start
+        pf_tiles.sort(key=lambda bt: -(starts[bt[0]] + bt[1]))
         Nt = len(pf_tiles)
         o_dr = o_rows + _align4(max(W, 1))
         o_ds = o_dr + _align4(max(Bd, 1))
