@@ -11,7 +11,10 @@
 //   warp 0, one lane: TMA.  Q once (two 64 x 64 boxes); the block's K and V page by page (a page
 //           of one kv head is a [page_size x 64] box of the cache seen as a 2-D tensor; pages
 //           past the context are asked for past the end of the tensor and arrive as zeros) into
-//           a ring of two stages, 128-byte swizzle.
+//           rings of two tiles for the keys and two for the values, 128-byte swizzle.  A key tile
+//           is free once its scores are done, a block earlier than its value tile: with one ring
+//           for both, the keys of the next block were asked for so late that the products waited
+//           for them (1.8 us a block and CTA, most of it that wait).
 //   warp 1, one lane: S = Q K^T (tcgen05.mma, M 128, N 128, K 64) into tensor memory; after the
 //           softmax warps have written P: O += P V (M 128, N 64, K 128; V is the MN-major
 //           operand, straight from the cache's layout), accumulated in tensor memory.
@@ -53,8 +56,8 @@ constexpr uint32_t IDESC_PV = idesc_bf16(TM, HD) | (1u << 16);      // B (V) is 
 
 struct PCtrl {
     uint64_t q_full;
-    uint64_t kv_full[KV_STAGES];
-    uint64_t kv_empty[KV_STAGES];
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];     // keys and values have rings of their own: a key
+    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];     // tile is free a whole block before its value tile
     uint64_t s_full, s_empty, p_full, o_full;
     uint32_t tmem_base;
     int abort;
@@ -148,8 +151,10 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         ctrl->abort = 0;
         bar_init(&ctrl->q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            bar_init(&ctrl->kv_full[s], 1);
-            bar_init(&ctrl->kv_empty[s], 1);
+            bar_init(&ctrl->k_full[s], 1);
+            bar_init(&ctrl->k_empty[s], 1);
+            bar_init(&ctrl->v_full[s], 1);
+            bar_init(&ctrl->v_empty[s], 1);
         }
         bar_init(&ctrl->s_full, 1);
         bar_init(&ctrl->s_empty, 4);
@@ -179,25 +184,32 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         }
         const int pages_per_blk = TN / page_size;
         const int page_bytes = page_size * HD * 2;
-        for (int it = 0; it < n_blk; ++it) {
+        // one tile (the keys or the values of block `it`): a page a lane
+        auto load_tile = [&](int it, bool is_v) {
             const int s = it % KV_STAGES;
-            if (it >= KV_STAGES && !bar_wait(&ctrl->kv_empty[s], ((it / KV_STAGES) - 1) & 1, &ctrl->abort)) break;
-            unsigned char* kt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES;
-            if (lane == 0) bar_expect_tx(&ctrl->kv_full[s], 2 * KV_TILE_BYTES);
+            uint64_t* full = is_v ? &ctrl->v_full[s] : &ctrl->k_full[s];
+            if (it >= KV_STAGES &&
+                !bar_wait(is_v ? &ctrl->v_empty[s] : &ctrl->k_empty[s], ((it / KV_STAGES) - 1) & 1, &ctrl->abort))
+                return false;
+            unsigned char* tile = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + (is_v ? KV_TILE_BYTES : 0);
+            if (lane == 0) bar_expect_tx(full, KV_TILE_BYTES);
             __syncwarp();
-            const int key0 = (blk_lo + it) * TN;
-            if (lane < 2 * pages_per_blk) {
-                const int p = lane % pages_per_blk;
-                const bool is_v = lane >= pages_per_blk;
-                const int key = key0 + p * page_size;
+            if (lane < pages_per_blk) {
+                const int key = (blk_lo + it) * TN + lane * page_size;
                 // a page past the context, or wholly behind the window of the tile's first token
                 // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
                 const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
                 const int row = wanted ? (table[key / page_size] * nkv + kvh) * page_size : cache_rows;
-                tma_load_2d(kt + (is_v ? KV_TILE_BYTES : 0) + (size_t)p * page_bytes, is_v ? &map_v : &map_k, 0, row,
-                            &ctrl->kv_full[s]);
+                tma_load_2d(tile + (size_t)lane * page_bytes, is_v ? &map_v : &map_k, 0, row, full);
             }
             __syncwarp();
+            return true;
+        };
+        // in the order they are wanted: the keys of a block are multiplied while the block before
+        // is in its softmax, its values only after its own
+        for (int it = 0; it <= n_blk; ++it) {
+            if (it < n_blk && !load_tile(it, false)) break;
+            if (it >= 1 && !load_tile(it - 1, true)) break;
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -205,7 +217,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             const uint64_t qdesc = smem_desc_sw128(q_tile);
             auto issue_s = [&](int it) {
                 const int s = it % KV_STAGES;
-                if (!bar_wait(&ctrl->kv_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) return false;
+                if (!bar_wait(&ctrl->k_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) return false;
                 // the softmax warps have taken the scores of the block before out of tensor memory
                 if (it > 0 && !bar_wait(&ctrl->s_empty, (it - 1) & 1, &ctrl->abort)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -214,6 +226,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                 for (int k = 0; k < HD / 16; ++k)
                     umma_bf16(tmem_s, qdesc + (uint64_t)(k * 32 >> 4), kdesc + (uint64_t)(k * 32 >> 4), IDESC_S, k != 0 ? 1u : 0u);
                 umma_commit(&ctrl->s_full);
+                umma_commit(&ctrl->k_empty[s]);
                 return true;
             };
             if (ok && n_blk > 0) ok = issue_s(0);
@@ -221,6 +234,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                 const int s = it % KV_STAGES;
                 if (it + 1 < n_blk && !issue_s(it + 1)) break;         // the next block's scores, behind this block's softmax
                 if (!bar_wait(&ctrl->p_full, it & 1, &ctrl->abort)) break;
+                if (!bar_wait(&ctrl->v_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned char* vt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
 #pragma unroll
@@ -231,7 +245,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                     umma_bf16(tmem_o, pdesc, vdesc, IDESC_PV, (it | k) != 0 ? 1u : 0u);     // O accumulates over the blocks
                 }
                 umma_commit(&ctrl->o_full);
-                umma_commit(&ctrl->kv_empty[s]);
+                umma_commit(&ctrl->v_empty[s]);
             }
         }
     } else {
@@ -317,7 +331,8 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             l_run += lsum;
             // Slots of the last page past the context hold whatever was there before; a zero of P
             // times a NaN would still be a NaN, so those rows of V are cleared (thread r: key r of
-            // the block; the tile has arrived, since the scores that needed K have)
+            // the block), once the tile has arrived
+            if (key0 + TN > ctx) ok = bar_wait(&ctrl->v_full[it % KV_STAGES], (it / KV_STAGES) & 1, &ctrl->abort) && ok;
             if (key0 + r >= ctx) {
                 uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES + (size_t)r * 128);
 #pragma unroll
