@@ -30,6 +30,11 @@
 // 1356 us.  One lane issuing a block's sixteen page copies: 972 us whatever the softmax warps did.
 // Eight softmax warps, two threads a row with a softmax stream and an accumulator each: 822 us.)
 //
+// A short portion of a long prompt is few tiles with many blocks each: 2 or 4 CTAs of a cluster then
+// take a tile's blocks in turn and rank 0 merges their rows through distributed shared memory
+// (a 256-token portion at 8192 tokens of context: 114 -> 54 us; with enough tiles to fill the SMs
+// the sharing only costs, so it is used when the CTAs fit the SMs at once).
+//
 // Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets the error word
 // (rlis_attention_prefill_tc_error), every role runs to its end without further waits, and the
 // CTA frees its tensor memory before it returns.
@@ -109,6 +114,28 @@ __device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int
     }
 }
 
+// 32 float32 sums of a row, times `inv`, as bf16 to `dst` (16-byte stores).
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], float inv, bf16* dst) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        uint4 pk;
+        pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+        pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+        pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+        pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+        *reinterpret_cast<uint4*>(dst + i) = pk;
+    }
+}
+// A row of the accumulated output from tensor memory, normalised, to `orow`.
+__device__ __forceinline__ void store_row(uint32_t tmem_row, float inv, bool pred, bf16* orow) {
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_row + (uint32_t)(c * 32), v);
+        if (pred) store_chunk(v, inv, orow + c * 32);
+    }
+}
+
 // A row's softmax reference may lag behind its maximum by this much (in powers of two) before the
 // accumulated output is rescaled: P then holds values up to 2^8, which bf16 and the float32 sums
 // take, and the rescaling of O in tensor memory becomes rare after the first blocks.
@@ -119,7 +146,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
     const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
-    int cache_rows, float scale, int window) {
+    int cache_rows, float scale, int window, int splits) {
     extern __shared__ __align__(1024) unsigned char pt_smem_raw[];
     if ((smem_u32(pt_smem_raw) & 1023u) != 0u) {       // the swizzled tiles need it; never seen, but checked
         if (threadIdx.x == 0) atomicExch(&g_tc_error, 2);
@@ -134,7 +161,8 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     const int nrep = nh / nkv;
     // x: the pair of heads, y: the tile; CTAs start in the order of the tile list across all heads
     const int b = tiles[2 * blockIdx.y], t0 = tiles[2 * blockIdx.y + 1];
-    const int head0 = blockIdx.x * 2;
+    const int head0 = (blockIdx.x / splits) * 2;
+    const int rank = blockIdx.x % splits;                    // of this CTA in its cluster: it takes blocks rank, rank + splits, ...
     const int kvh = head0 / nrep;
     const int q_start = cu_seqlens[b];
     const int q_len = cu_seqlens[b + 1] - q_start;
@@ -145,7 +173,9 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     const int last_pos = pos0 + n_valid - 1;
     const int blk_lo = window > 0 ? max(0, pos0 - window + 1) / TN : 0;
     const int blk_hi = last_pos / TN;                        // inclusive
-    const int n_blk = blk_hi - blk_lo + 1;
+    const int n_blk_all = blk_hi - blk_lo + 1;
+    const int n_blk = rank < n_blk_all ? (n_blk_all - rank + splits - 1) / splits : 0;
+    const int blk0 = blk_lo + rank;
 
     if (threadIdx.x == 0) {
         ctrl->abort = 0;
@@ -171,6 +201,11 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = ctrl->tmem_base;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u;
+    // warps 2-5: warp w reads TMEM lanes 32 (w % 4) .. + 31; a lane is a row of the tile
+    const int srow = (warp & 3) * 32 + lane;
+    const uint32_t slane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    float m_ref = -INFINITY, l_run = 0.f;       // the reference of the row's exponentials so far, and their sum
+    bool row_ok = true;
     pdl_wait();             // q and this portion's keys come from the kernels before
 
     if (warp == 0) {
@@ -195,7 +230,7 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             if (lane == 0) bar_expect_tx(full, KV_TILE_BYTES);
             __syncwarp();
             if (lane < pages_per_blk) {
-                const int key = (blk_lo + it) * TN + lane * page_size;
+                const int key = (blk0 + it * splits) * TN + lane * page_size;
                 // a page past the context, or wholly behind the window of the tile's first token
                 // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
                 const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
@@ -249,20 +284,16 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             }
         }
     } else {
-        // softmax and output: warp w reads TMEM lanes 32 (w % 4) .. + 31; a lane is a row
-        const int q4 = warp & 3;
-        const int r = q4 * 32 + lane;
-        const int hsel = r >> 6, qi = r & 63;
-        const int pos = pos0 + qi;
+        // softmax and output
+        const int r = srow;
+        const int pos = pos0 + (srow & 63);
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-        const bool row_valid = qi < n_valid;
-        const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
+        const uint32_t lane_addr = slane_addr;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float m_ref = -INFINITY, l_run = 0.f;       // the reference of the exponentials so far, and their sum
         unsigned char* prow = p_tile + (size_t)r * 128;          // this row's 128-byte line in each half
         bool ok = true;
         for (int it = 0; it < n_blk; ++it) {
-            const int key0 = (blk_lo + it) * TN;
+            const int key0 = (blk0 + it * splits) * TN;
             ok = bar_wait(&ctrl->s_full, it & 1, &ctrl->abort) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // the whole row of scores at once, and tensor memory is free for the next block's scores
@@ -347,23 +378,86 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         if (n_blk > 0) {
             ok = bar_wait(&ctrl->o_full, (n_blk - 1) & 1, &ctrl->abort) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = 1.0f / l_run;
-            bf16* orow = out + ((size_t)(q_start + t0 + qi) * nh + head0 + hsel) * HD;
+        }
+        row_ok = ok;
+    }
+    // the row's place in the output: head (srow / 64) of the pair, token (srow % 64) of the tile
+    const bool srow_valid = (srow & 63) < n_valid;
+    bf16* sorow = out + ((size_t)(q_start + t0 + (srow & 63)) * nh + head0 + (srow >> 6)) * HD;
+    if (splits == 1) {
+        if (warp >= 2 && n_blk > 0) store_row(tmem_o + slane_addr, 1.0f / l_run, row_ok && srow_valid, sorow);
+    } else {
+        // The CTAs of the cluster took the blocks of keys in turn.  Once all their products are done
+        // (the tiles in shared memory are free), ranks 1.. send their rows (64 unnormalised sums,
+        // the reference of the exponentials and their sum) into rank 0's tiles; rank 0 brings them
+        // to one reference in the order of the ranks, adds, normalises and stores.
+        constexpr int ROW_F = 68;                      // floats a row in the exchange area (16-byte aligned rows)
+        float* xchg = reinterpret_cast<float*>(pt_smem_raw);
+        __syncwarp();
+        cluster_sync_all();
+        if (warp >= 2 && rank > 0) {
+            float* dst = xchg + ((size_t)(rank - 1) * TM + srow) * ROW_F;
+            uint32_t raddr;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(dst)), "r"(0));
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
-                if (ok && row_valid) {
+                if (n_blk > 0) {
+                    tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 pk;
-                        pk.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-                        pk.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-                        pk.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-                        pk.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = pk;
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;            // no block of its own: nothing was accumulated
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr + (uint32_t)((c * 32 + i) * 4)),
+                                 "r"(v[i]), "r"(v[i + 1]), "r"(v[i + 2]), "r"(v[i + 3]) : "memory");
+            }
+            asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(raddr + (uint32_t)(HD * 4)),
+                         "r"(__float_as_uint(m_ref)), "r"(__float_as_uint(row_ok ? l_run : __int_as_float(0x7fc00000))) : "memory");
+        }
+        __syncwarp();
+        cluster_sync_all();
+        if (warp >= 2 && rank == 0) {
+            float m = m_ref;
+            for (int k = 1; k < splits; ++k) m = fmaxf(m, xchg[((size_t)(k - 1) * TM + srow) * ROW_F + HD]);
+            const float f0 = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m);
+            float l = l_run * f0;
+            float fk[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 1; k < 4; ++k) {
+                if (k < splits) {
+                    const float* src = xchg + ((size_t)(k - 1) * TM + srow) * ROW_F;
+                    fk[k - 1] = src[HD] == -INFINITY ? 0.f : ex2_approx(src[HD] - m);
+                    l += src[HD + 1] * fk[k - 1];
+                }
+            }
+            const float inv = 1.0f / l;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t v[32];
+                if (n_blk > 0) {
+                    tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f0);
+#pragma unroll
+                for (int k = 1; k < 4; ++k) {
+                    if (k >= splits) continue;
+                    const float4* src = reinterpret_cast<const float4*>(xchg + ((size_t)(k - 1) * TM + srow) * ROW_F + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 o = src[i];
+                        v[4 * i] = __float_as_uint(fmaf(o.x, fk[k - 1], __uint_as_float(v[4 * i])));
+                        v[4 * i + 1] = __float_as_uint(fmaf(o.y, fk[k - 1], __uint_as_float(v[4 * i + 1])));
+                        v[4 * i + 2] = __float_as_uint(fmaf(o.z, fk[k - 1], __uint_as_float(v[4 * i + 2])));
+                        v[4 * i + 3] = __float_as_uint(fmaf(o.w, fk[k - 1], __uint_as_float(v[4 * i + 3])));
                     }
                 }
+                if (row_ok && srow_valid && l == l) store_chunk(v, inv, sorow + c * 32);
             }
         }
     }
@@ -388,9 +482,14 @@ bool make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long long co
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+int g_pf_splits = 0;      // 0: chosen from the number of tiles and the longest context
 }  // namespace
 
 extern "C" int rlis_attention_prefill_tc_error(void) { return tc::read_error_word(); }
+
+// 0: automatic; 1, 2 or 4: the CTAs that share a tile's keys.  For measurements.
+extern "C" void rlis_attention_prefill_tc_set_splits(int splits) { g_pf_splits = splits; }
 
 // Whether the tensor-core kernel takes these sizes (else the caller uses rlis_attention_prefill).
 extern "C" int rlis_attention_prefill_tc_takes(int nh, int nkv, int d, int page_size) {
@@ -400,12 +499,13 @@ extern "C" int rlis_attention_prefill_tc_takes(int nh, int nkv, int d, int page_
 }
 
 // q, out [tokens, nh * 64]; caches [pages, nkv, page_size, 64]; tiles [n_tiles, 2] = (batch entry,
-// first token of 64) as for rlis_attention_prefill.
+// first token of 64) as for rlis_attention_prefill; max_ctx: the longest context among the
+// requests of the step, or 0.
 extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                          const int* tiles, int n_tiles, const int* cu_seqlens,
                                          const int* ctx_lens, const int* block_tables, int max_blocks,
                                          int n_tokens, int n_pages, int nh, int nkv, int d, int page_size,
-                                         float scale, int window, int dtype, cudaStream_t stream) {
+                                         float scale, int window, int dtype, int max_ctx, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (dtype != RLIS_BF16 || !rlis_attention_prefill_tc_takes(nh, nkv, d, page_size) || n_tiles > 65535)
         return RLIS_ERR_UNSUPPORTED;
@@ -424,8 +524,22 @@ extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, con
         cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM);
         attr_done = true;
     }
-    rlis_launch(attn_prefill_tc_kernel, dim3((unsigned)(nh / 2), (unsigned)n_tiles), PT_THREADS, PT_SMEM, stream,
-                map_q, map_k, map_v, (bf16*)out, tiles, cu_seqlens, ctx_lens, block_tables, max_blocks, nh, nkv,
-                page_size, (int)cache_rows, scale, window);
+    // Few tiles with many keys each (a short portion of a long prompt) would leave SMs idle, and the
+    // tiles at the end of a prompt run long after the others are done: 2 or 4 CTAs of a cluster then
+    // share a tile's blocks of keys.  max_ctx: the longest context of the step (0: unknown, no sharing).
+    int splits = g_pf_splits;
+    if (splits <= 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long ctas = (long long)n_tiles * (nh / 2);
+        const int blocks = window > 0 ? (window + TQ + TN - 1) / TN + 1 : (max_ctx + TN - 1) / TN;
+        splits = 1;
+        // measured: it pays while the CTAs still fit the SMs at once (two each) and every one keeps 8 blocks
+        while (splits < 4 && ctas * splits * 2 <= 2ll * sms && blocks >= 16 * splits) splits *= 2;
+    }
+    if (splits != 1 && splits != 2 && splits != 4) return RLIS_ERR_UNSUPPORTED;
+    rlis_launch_cluster(attn_prefill_tc_kernel, dim3((unsigned)(nh / 2 * splits), (unsigned)n_tiles), PT_THREADS, PT_SMEM,
+                        stream, dim3((unsigned)splits, 1, 1), map_q, map_k, map_v, (bf16*)out, tiles, cu_seqlens,
+                        ctx_lens, block_tables, max_blocks, nh, nkv, page_size, (int)cache_rows, scale, window, splits);
     return RLIS_LAUNCH_CHECK();
 }

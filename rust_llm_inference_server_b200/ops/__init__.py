@@ -437,10 +437,12 @@ PREFILL_TCGEN05 = True     # False: the mma.sync kernel for every size (measurem
 
 def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,
                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                      window: int = 0) -> torch.Tensor:
+                      window: int = 0, max_ctx: int = 0) -> torch.Tensor:
     """Causal flash attention of portions of prompts over the paged cache (bfloat16, head sizes 64
     and 128).  tiles int32 [n, 2] = (batch entry, first token of the 64-token tile within the
-    entry's portion); cu_seqlens int32 [B + 1] = rows of the entries' first tokens."""
+    entry's portion); cu_seqlens int32 [B + 1] = rows of the entries' first tokens.  max_ctx: the
+    longest context of the step if known (with few tiles and long contexts several CTAs then
+    share a tile's keys)."""
     _req(q, "q", torch.bfloat16, (None, n_heads * head_dim))
     _req(out, "out", torch.bfloat16, tuple(q.shape))
     _req(k_cache, "k_cache", torch.bfloat16, (None, n_kv_heads, page_size, head_dim))
@@ -457,7 +459,7 @@ def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, blo
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
             tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),
             block_tables.shape[1], q.shape[0], k_cache.shape[0], n_heads, n_kv_heads, head_dim, page_size,
-            float(scale), int(window), _code(q.dtype), _stream()), "attention_prefill_tc")
+            float(scale), int(window), _code(q.dtype), int(max_ctx), _stream()), "attention_prefill_tc")
         _count()
         return out
     check(lib().rlis_attention_prefill(
@@ -488,7 +490,8 @@ def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_hea
                          n_heads, n_kv_heads, head_dim, page_size, scale, window, splits, scratch)
     if pf_fast:
         attention_prefill(q, k_cache, v_cache, out, step.prefill_tiles, step.cu_seqlens, step.ctx_lens,
-                          tables, n_heads, n_kv_heads, head_dim, page_size, scale, window)
+                          tables, n_heads, n_kv_heads, head_dim, page_size, scale, window,
+                          getattr(step, "max_ctx_len", 0))
     if dec_fast and pf_fast:
         return out
     if not dec_fast and not pf_fast:

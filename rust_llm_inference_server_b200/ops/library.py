@@ -31,7 +31,7 @@ SIGNATURES = {
     "rlis_attention_decode_pages": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_decode_qkv": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P],
-    "rlis_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+    "rlis_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_attention_prefill_tc_takes": [I, I, I, I],
     "rlis_repetition_penalty": [P, P, P, P, P, I, I, LL, P],
     "rlis_sample_rows": [P, P, P, I, I, LL, P],
@@ -66,6 +66,8 @@ def lib():
             fn.restype = c_int
         handle.rlis_gemm_tcgen05_error.argtypes = []
         handle.rlis_gemm_tcgen05_error.restype = c_int
+        handle.rlis_attention_prefill_tc_set_splits.argtypes = [c_int]
+        handle.rlis_attention_prefill_tc_set_splits.restype = None
         handle.rlis_attention_prefill_tc_error.argtypes = []
         handle.rlis_attention_prefill_tc_error.restype = c_int
         handle.rlis_stream_gemm_error.argtypes = []

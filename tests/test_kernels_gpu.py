@@ -399,11 +399,21 @@ def test_prefill_flash_attention_over_pages(geom, ps, window):
     q, kc, vc, tables, sot, pos, want = attention_case(geom, lens, q_lens, ps, torch.bfloat16, window=window, seed=d + ps)
     tiles = torch.tensor([(b, t0) for b, n in enumerate(q_lens) for t0 in range(0, n, 64)], dtype=torch.int32)
     cu = torch.tensor(np.cumsum([0] + q_lens), dtype=torch.int32)
-    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
-    ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu), dev(torch.tensor(lens, dtype=torch.int32)),
-                          dev(tables), nh, nkv, d, ps, 1 / math.sqrt(d), window or 0)
-    err = (out.float().cpu().view(-1, nh, d) - want).abs().max()
-    assert err <= 2.5e-2, err
+    from rust_llm_inference_server_b200.ops.library import lib
+    try:
+        # the tcgen05 kernel lets 1, 2 or 4 CTAs of a cluster share a tile's blocks of keys (some then
+        # have no block at all); 0: its own choice from the number of tiles and the longest context
+        for splits in (1, 2, 4, 0):
+            lib().rlis_attention_prefill_tc_set_splits(splits)
+            out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+            ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu),
+                                  dev(torch.tensor(lens, dtype=torch.int32)), dev(tables), nh, nkv, d, ps,
+                                  1 / math.sqrt(d), window or 0, max(lens))
+            err = (out.float().cpu().view(-1, nh, d) - want).abs().max()
+            assert err <= 2.5e-2, (splits, err)
+    finally:
+        lib().rlis_attention_prefill_tc_set_splits(0)
+    ops.check_device_errors()
 
 
 def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
@@ -415,9 +425,10 @@ def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
     for qi, key, seen in ((0, 3, True), (0, 800, True), (0, 801, False), (150, 950, True), (150, 951, False),
                           (199, 999, True), (64, 864, True), (63, 864, False), (100, 15, True), (100, 16, True)):
         q, kc, vc, tables, sot, pos, want = attention_case(geom, [n], [m], ps, torch.bfloat16, seed=key, spike=(0, qi, key))
+        # few tiles and a long context: the kernel shares each tile's keys among the CTAs of a cluster
         out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
         ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu), dev(torch.tensor([n], dtype=torch.int32)),
-                              dev(tables), 8, 2, 64, ps, 0.125, 0)
+                              dev(tables), 8, 2, 64, ps, 0.125, 0, n)
         got = out.float().cpu().view(m, 8, 64)
         assert (got - want).abs().max() <= 3e-2
         assert ((got[qi] - 7.0).abs().max() < 0.05) == seen, (qi, key)
