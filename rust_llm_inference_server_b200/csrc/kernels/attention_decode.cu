@@ -774,7 +774,9 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
         // Stages of K/V a warp keeps: what shared memory allows for the CTAs to be resident together
         // (bytes in flight an SM are what the kernel's rate is made of; see the file's head).
         int stages = g_decode_stages;
-        if (stages == 0) stages = ctas <= 2 * sms ? 3 : 2;     // (four stages, one CTA an SM, measured slower at every size)
+        // three stages (two CTAs an SM) unless two (three CTAs an SM) get the grid through in
+        // fewer rounds (four stages, one CTA an SM, measured slower at every size)
+        if (stages == 0) stages = (ctas + 2 * sms - 1) / (2 * sms) <= (ctas + 3 * sms - 1) / (3 * sms) ? 3 : 2;
         if (d == 128 && stages > 3) stages = 3;               // 4 stages of 128-wide rows do not fit
         // Head size 64 with pages of 8 tokens or more (that divide, or are divided by, a block of 32
         // keys): the keys come by bulk tensor copies into swizzled tiles.  Needs the number of pages

@@ -340,16 +340,21 @@ DECODE_MIN_KEYS_PER_SPLIT = 128
 @functools.lru_cache(maxsize=4096)
 def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
     """How many pieces the context is cut into for decode attention (role of `split_plan`,
-    crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs): enough CTAs
-    (kv heads x requests x splits) to fill the SMs about twice, four pieces for long contexts in
-    any case (it evens out the tail of large batches), each piece at least 128 keys long.  Up to
-    8 pieces of a small grid are merged inside a thread-block cluster, and clusters of 2, 4 and 8
-    are the sizes that schedule well (batch 8, context 4096: 17.4 us with 4 pieces, 29.2 with 5)."""
+    crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs).  Few requests:
+    enough CTAs (kv heads x requests x pieces) to fill the SMs about twice, each piece at least
+    128 keys long.  From 64 (request, kv head) pairs on, pieces of at least 512 keys and no more
+    than about 384 CTAs; from 256 pairs on, one piece at every context: the pairs fill the SMs by
+    themselves, and cutting only adds the merge (batch 32, context 2048: 22.6 us whole, 33.8 us
+    in 4 pieces; batch 64, context 4096: 82.5 against 95.9 us).  Up to 8 pieces of a small grid are
+    merged inside a thread-block cluster, and clusters of 2, 4 and 8 are the sizes that schedule
+    well (batch 8, context 4096: 17.4 us with 4 pieces, 29.2 with 5)."""
     groups = max(1, n_decode * n_kv_heads)
     want = -(-2 * NUM_SMS // groups)
-    if groups * 4 > DECODE_CLUSTER_MAX_CTAS:
-        want = max(want, min(4, max_ctx // 512))
-    want = max(1, min(want, max_ctx // DECODE_MIN_KEYS_PER_SPLIT, 32))
+    min_keys = DECODE_MIN_KEYS_PER_SPLIT
+    if groups >= 64:
+        want = min(want, max(1, 384 // groups))
+        min_keys = 512
+    want = max(1, min(want, max_ctx // min_keys, 32))
     if want > 1 and groups * min(want, 8) <= DECODE_CLUSTER_MAX_CTAS:
         # merged inside a cluster: 2, 4 or 8 pieces; with few requests 8, until a piece gets long
         # (batch 1, context 4096: 6.7 us with 8 pieces in a cluster, 12.6 us with 32 and tickets)
