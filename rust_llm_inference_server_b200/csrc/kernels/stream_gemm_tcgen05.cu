@@ -12,7 +12,7 @@
 //     tensor memory; tcgen05.commit frees the stage;
 //   * four warps read the accumulator (a lane = a feature, a column = a token) and store.
 // Matrices with few features would fill few SMs, so k is split over the CTAs of a thread-block
-// cluster (grid = feature tiles x splits, 2 to 16 splits, more CTAs than SMs and all resident at
+// cluster (grid = feature tiles x splits, up to 16 splits, about two CTAs an SM and all resident at
 // once: the whole matrix is requested in the first microsecond).  After a cluster barrier (all
 // products done, the stages free) each CTA sends its float32 partial sums of token t into the
 // shared memory of CTA t % splits (st.async, counted on that CTA's mbarrier), which adds the rows
@@ -308,7 +308,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     }
 }
 
-int g_target_ctas = 0;      // 0: 1.3 times the number of SMs
+int g_target_ctas = 0;      // 0: twice the number of SMs
 
 template <int NT, int EPI, typename OutT>
 int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, const NormFuse& nf, cudaStream_t stream) {
@@ -326,13 +326,18 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, co
     if (target <= 0) {
         int dev = 0, sms = 148;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        target = sms + sms * 3 / 10;
+        target = 2 * sms;
     }
-    // splits (a power of two, the cluster's size) from N and K alone: enough CTAs for the SMs, at
-    // least two stages of k each
-    int splits = 1;
-    while (splits < MAX_SPLITS && tiles * splits < target && k_blocks >= 4 * splits) splits *= 2;
+    // splits (the cluster's size, any number up to 16) from N and K alone: about two CTAs an SM, at
+    // least two stages of k each, and no split without work.  (Measured in the decode step of a 1B
+    // Llama, batch 8: gate|up, 128 tiles, in 3 splits instead of 2: -29 us a step, in 4: +46 us;
+    // the O projection, 16 tiles and 32 blocks of k, in 16 instead of 8: -15 us.)
+    int splits = (target + tiles - 1) / tiles;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+    if (splits > k_blocks / 2) splits = k_blocks / 2;
+    if (splits < 1) splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per - 1) / per;
     rlis_launch_cluster(stream_gemm_kernel<NT, EPI, OutT>, dim3((unsigned)tiles, (unsigned)splits), S_THREADS,
                         stream_smem_bytes<NT>(), stream, dim3(1, (unsigned)splits, 1), map_w, map_x, (OutT*)y, M, N, K,
                         per, nf);
@@ -351,7 +356,7 @@ int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, 
 
 extern "C" int rlis_stream_gemm_error(void) { return tc::read_error_word(); }
 
-// About how many CTAs a launch is cut into (0: 1.3 times the SMs).  For measurements.
+// About how many CTAs a launch is cut into (0: twice the SMs).  For measurements.
 extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }
 
 // out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (SwiGLU, rows of W interleaved
