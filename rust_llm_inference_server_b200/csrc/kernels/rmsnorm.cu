@@ -123,7 +123,10 @@ extern "C" int rlis_rmsnorm(float* resid, const void* delta, const float* w, voi
                             const int* rows, int n_tokens, int hidden, float eps, int dtype,
                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    // many rows (portions of prompts): fewer threads with four vectors each keep more loads in
+    // flight an SM (2048 rows of 2048: a 2048-token prefill of 16 layers 4.72 -> 4.64 ms)
+    if (n_tokens > 64 && (hidden & 3) == 0) threads = min(threads, max(128, ((hidden + 15) / 16 + 31) / 32 * 32));
     if ((hidden & 3) == 0 && hidden <= threads * 16) {
         if (dtype == RLIS_F32)
             rlis_launch(rmsnorm_vec4_kernel<float>, n_tokens, threads, 0, stream, resid, (const float*)delta, w, (float*)out, rows, hidden, eps);

@@ -88,6 +88,8 @@ def lib():
         handle.rlis_set_pdl.restype = None
         if os.environ.get("RLIS_PDL", "1") == "0":      # programmatic dependent launch is on unless switched off
             handle.rlis_set_pdl(0)
+        if os.environ.get("RLIS_STREAM_CTAS"):           # for measurements: CTAs a streaming product is cut into
+            handle.rlis_stream_gemm_set_target(int(os.environ["RLIS_STREAM_CTAS"]))
         _lib = handle
     return _lib
 
