@@ -83,6 +83,29 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, dtype):
         worst = max(float(np.abs(v - whole[k]).max()) for k, v in sub.items())
         assert worst <= TOL_BETWEEN_MODES[dtype], f"{which} {dtype}: {fam} differs from whole by {worst}"
 
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_norms_inside_the_products_and_norms_as_kernels_agree(model_root, which, monkeypatch):
+    """Steps of up to 16 rows take the norms apart into the epilogues of the products around them
+    (`ops.ScaledRows`, `ops.ResidualSink`); with that switched off every norm is a kernel of its
+    own.  Both ways: the plain logits, each other to rounding, and fewer launches with it on."""
+    from rust_llm_inference_server_b200 import ops
+    reqs = requests_for(which)
+    ref = plain_logits(model_root, which)
+    steps = R.decode_trace(reqs)
+    got, launches = {}, {}
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "FUSE_NORMS", fused)
+        s = session(model_root, which, "bfloat16", R.live_token_peak(steps))
+        s.model.graph_safe = False           # count launches, not graph replays
+        before = ops.launch_count
+        got[fused] = R.collect(s.step, steps)
+        launches[fused] = ops.launch_count - before
+        compare(got[fused], ref, TOL["bfloat16"], f"{which} norms {'inside' if fused else 'as kernels'} vs plain")
+    worst = max(float(np.abs(v - got[False][k]).max()) for k, v in got[True].items())
+    assert worst <= TOL_BETWEEN_MODES["bfloat16"], worst
+    if CONFIGS[which]["hidden_size"] % 8 == 0 and CONFIGS[which]["intermediate_size"] % 8 == 0:
+        assert launches[True] < launches[False]
+
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(model_root, dtype):
