@@ -35,8 +35,8 @@
 // Sending a row of partial sums as one bulk copy from a staging area in shared memory, counted once
 // on the finisher's mbarrier, instead of 128 counted stores, with the cluster barrier at the end
 // that the staging area then needs: 5.6 -> 6.6 us for the QKV product of 8 rows, the step 0.87 ->
-// 0.93 ms.  With 17 rows and more (x tiles of 32 rows) a product takes twice as long as with 16
-// in either form, so longer batches go to the library GEMM.)
+// 0.93 ms.  With 17 to 32 rows a layer's four products take 46 us, with 64 rows 64 us, against 39 us
+// for the library (plus its gating and norm kernels), so longer batches go to the library GEMM.)
 //
 // Epilogues: bf16 or float32 y, or SwiGLU on a gate|up matrix whose rows are interleaved in blocks
 // of 4 (rows 8t..8t+3 gate, 8t+4..8t+7 up): y[m, 4t + j] = silu(gate_j) * up_j.
@@ -62,13 +62,20 @@ namespace {
 using namespace tc;
 constexpr int SF = 128;                 // features of a CTA (the M side of the instruction)
 constexpr int SK = 64;                  // k of a stage: 128 bytes of bf16, one swizzle row
-constexpr int S_STAGES = 4;
+constexpr int S_STAGES = 4;             // with x tiles of 16 rows; see stages_of
+// Stages of the ring by the rows of the x tile.  Three CTAs have to fit an SM (the clusters of two
+// kernels are resident at the same time): with four stages and x tiles of 32 rows only two did,
+// and a product of 17 to 32 rows took twice as long as one of 16 (a layer's four products:
+// 76 us; with three stages 46 us, with two 54 us).  The stages also hold the rows that the
+// cluster sends for the reduction, up to NT + 15 of them (checked in the kernel): two stages of
+// 128-row tiles are too small for that.
+template <int NT> __host__ __device__ constexpr int stages_of() { return NT <= 16 ? S_STAGES : 3; }
 constexpr int W_STAGE_BYTES = SF * SK * 2;
 constexpr int S_THREADS = 128;
 constexpr int MAX_SPLITS = 16;          // the largest cluster (above 8 is opt-in)
 
 template <int NT> constexpr size_t stream_smem_bytes() {
-    return (size_t)S_STAGES * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
+    return (size_t)stages_of<NT>() * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
 }
 
 struct SCtrl {
@@ -145,8 +152,11 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
     constexpr uint32_t IDESC = idesc_bf16(SF, NT);
     unsigned char* w_tiles = base;
-    unsigned char* x_tiles = base + (size_t)S_STAGES * W_STAGE_BYTES;
-    SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)S_STAGES * X_STAGE_BYTES);
+    constexpr int STG = stages_of<NT>();
+    static_assert((size_t)(NT + MAX_SPLITS - 1) * SF * 4 <= (size_t)STG * (W_STAGE_BYTES + NT * SK * 2),
+                  "the stages must hold the rows of partial sums that the cluster sends");
+    unsigned char* x_tiles = base + (size_t)STG * W_STAGE_BYTES;
+    SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)STG * X_STAGE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
@@ -158,7 +168,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
 
     if (threadIdx.x == 0) {
         ctrl->abort = 0;
-        for (int s = 0; s < S_STAGES; ++s) {
+        for (int s = 0; s < STG; ++s) {
             bar_init(&ctrl->full[s], 1);
             bar_init(&ctrl->empty[s], 1);
         }
@@ -186,7 +196,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         // stages of W are requested before this grid's dependency on the previous kernel of the
         // stream is resolved (programmatic dependent launch); x and y wait for it.
         const int n_kb = kb1 - kb0;
-        const int early = n_kb < S_STAGES ? n_kb : S_STAGES;
+        const int early = n_kb < STG ? n_kb : STG;
         for (int it = 0; it < early; ++it) {
             bar_expect_tx(&ctrl->full[it], W_STAGE_BYTES + X_STAGE_BYTES);
             tma_load_2d(w_tiles + (size_t)it * W_STAGE_BYTES, &map_w, (kb0 + it) * SK, n0, &ctrl->full[it]);
@@ -195,8 +205,8 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         for (int it = 0; it < early; ++it)
             tma_load_2d(x_tiles + (size_t)it * X_STAGE_BYTES, &map_x, (kb0 + it) * SK, 0, &ctrl->full[it]);
         for (int it = early; it < n_kb; ++it) {
-            const int s = it % S_STAGES, kb = kb0 + it;
-            if (!bar_wait(&ctrl->empty[s], ((it / S_STAGES) - 1) & 1, &ctrl->abort)) break;
+            const int s = it % STG, kb = kb0 + it;
+            if (!bar_wait(&ctrl->empty[s], ((it / STG) - 1) & 1, &ctrl->abort)) break;
             bar_expect_tx(&ctrl->full[s], W_STAGE_BYTES + X_STAGE_BYTES);
             tma_load_2d(w_tiles + (size_t)s * W_STAGE_BYTES, &map_w, kb * SK, n0, &ctrl->full[s]);
             tma_load_2d(x_tiles + (size_t)s * X_STAGE_BYTES, &map_x, kb * SK, 0, &ctrl->full[s]);
@@ -204,8 +214,8 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         pdl_trigger();     // everything this CTA reads is requested: the next kernel may start its own requests
     } else if (warp == 1 && lane == 0) {
         for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
-            const int s = it % S_STAGES;
-            if (!bar_wait(&ctrl->full[s], (it / S_STAGES) & 1, &ctrl->abort)) break;
+            const int s = it % STG;
+            if (!bar_wait(&ctrl->full[s], (it / STG) & 1, &ctrl->abort)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t adesc = smem_desc_sw128(w_tiles + (size_t)s * W_STAGE_BYTES);
             const uint64_t bdesc = smem_desc_sw128(x_tiles + (size_t)s * X_STAGE_BYTES);
