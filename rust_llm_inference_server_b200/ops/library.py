@@ -90,6 +90,8 @@ def lib():
             handle.rlis_set_pdl(0)
         if os.environ.get("RLIS_STREAM_CTAS"):           # for measurements: CTAs a streaming product is cut into
             handle.rlis_stream_gemm_set_target(int(os.environ["RLIS_STREAM_CTAS"]))
+        if os.environ.get("RLIS_DECODE_STAGES"):         # for measurements: stages of keys in decode attention
+            handle.rlis_attention_decode_set_stages(int(os.environ["RLIS_DECODE_STAGES"]))
         _lib = handle
     return _lib
 
