@@ -17,7 +17,7 @@ def test_decode_attention_pieces_by_batch_and_context():
             if n * kv * min(s, 8) <= ops.DECODE_CLUSTER_MAX_CTAS and s > 1:
                 assert s & (s - 1) == 0                          # merged in a cluster: a power of two
             last = s
-    assert ops.decode_splits(8, kv, 4096) == 4 and ops.decode_splits(1, kv, 4096) == 8
+    assert ops.decode_splits(8, kv, 4096) == 4 and ops.decode_splits(1, kv, 4096) == 8 and ops.decode_splits(2, kv, 4096) == 8
     assert ops.decode_splits(16, kv, 4096) == 2 and ops.decode_splits(8, kv, 512) == 1
     # the rule is a function of the step's shape only: the same step, the same pieces
     assert ops.decode_splits(3, 2, 7000) == ops.decode_splits(3, 2, 7000)
