@@ -164,6 +164,8 @@ PYBIND11_MODULE(_rlis_host, m) {
         .def("advance", &Scheduler::advance)
         .def("append_token", &Scheduler::append_token)
         .def("set_token", &Scheduler::set_token)
+        .def("drop_last_token", &Scheduler::drop_last_token)
+        .def("num_tokens", &Scheduler::num_tokens)
         .def("is_caught_up", &Scheduler::is_caught_up)
         .def("remove", &Scheduler::remove)
         .def("tokens", &Scheduler::tokens)

@@ -95,8 +95,23 @@ public:
         }
     }
 
+    // A request that was preempted since its last step still takes the token that step sampled.
     void append_token(SeqId id, int32_t token) {
-        if (SeqState* s = find_running(id)) s->tokens.push_back(token);
+        if (SeqState* s = find_any_mutable(id)) s->tokens.push_back(token);
+    }
+
+    // Takes back the newest token (a placeholder of a step that was planned but never launched).
+    // Tokens that have been computed stay.
+    void drop_last_token(SeqId id) {
+        SeqState* s = find_any_mutable(id);
+        if (!s || s->tokens.size() <= 1 || s->tokens.size() <= s->num_computed)
+            throw std::logic_error("drop_last_token: no uncomputed token to take back");
+        s->tokens.pop_back();
+    }
+
+    size_t num_tokens(SeqId id) const {
+        const SeqState* s = find_any(id);
+        return s ? s->tokens.size() : 0;
     }
 
     // Replaces the token at `index` (a placeholder that was appended for a step launched before

@@ -687,6 +687,7 @@ __device__ int g_decode_tickets[kMaxTickets];
 int g_decode_tma = 1;        // 0: 16-byte asynchronous copies for every size (measurements)
 int g_decode_cluster = 1;    // 0: merge through global memory and tickets even where a cluster could (measurements)
 int g_decode_stages = 0;     // 0: chosen from the grid; 2..4 for measurements (rlis_attention_decode_set_stages)
+int g_decode_last_variant = 0;   // of the last launch: bit 0 tensor-core kernel, bit 1 keys by TMA, bit 2 cluster merge
 
 template <int D, int NSTAGE, bool TMA> constexpr size_t decode_mma_smem_bytes() {
     return (size_t)DEC_WARPS * NSTAGE * 2 * 32 * (TMA ? D : D + 8) * sizeof(bf16);
@@ -724,10 +725,14 @@ size_t decode_smem_bytes(int nrep, int d) {
 }  // namespace
 
 // Floats of scratch that `rlis_attention_decode` needs for these sizes (0 when splits == 1).
+// Which kernel the last launch of this file took (for tests): bit 0 the tensor-core kernel, bit 1
+// keys by bulk tensor copies, bit 2 pieces merged in a cluster, bits 4.. stages of keys.
+extern "C" int rlis_attention_decode_last_variant(void) { return g_decode_last_variant; }
 extern "C" void rlis_attention_decode_set_stages(int stages) { g_decode_stages = stages; }
 extern "C" void rlis_attention_decode_set_cluster(int on) { g_decode_cluster = on; }
 extern "C" void rlis_attention_decode_set_tma(int on) { g_decode_tma = on; }
 extern "C" int rlis_attention_decode_error(void) { return tc::read_error_word(); }
+extern "C" int* rlis_attention_decode_error_addr(void) { return tc::error_word_addr(); }
 
 
 extern "C" long long rlis_attention_decode_scratch_floats(int n_decode, int nh, int d, int splits) {
@@ -824,11 +829,13 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
         }
 #undef LAUNCH_MMA
         launched = true;
+        g_decode_last_variant = 1 | (tma ? 2 : 0) | (cluster ? 4 : 0) | (stages << 4);
     }
 #define LAUNCH(N)                                                                                   \
     rlis_launch(attn_decode_kernel<N>, grid, DEC_THREADS, smem, stream,                                      \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, dec_rows,  \
         dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, d, page_size, scale, window, splits)
+    if (!launched) g_decode_last_variant = 0;
     if (!launched) switch (nrep) {
         case 1: LAUNCH(1); break;
         case 2: LAUNCH(2); break;

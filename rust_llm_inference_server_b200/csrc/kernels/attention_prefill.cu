@@ -22,6 +22,7 @@ namespace {
 constexpr int PF_WARPS = 4;
 constexpr int PF_THREADS = PF_WARPS * 32;
 constexpr int PF_BM = 64;   // query tokens per CTA
+static_assert(PF_BM == RLIS_PREFILL_TILE, "the host's tile list is cut for another tile size");
 constexpr int PF_BN = 64;   // keys per tile
 
 template <int D>
@@ -264,3 +265,6 @@ extern "C" int rlis_attention_prefill(const void* q, const void* k_cache, const 
             block_tables, max_blocks, nh, nkv, page_size, scale, window);
     return RLIS_LAUNCH_CHECK();
 }
+
+// Tokens a tile of the `tiles` list covers, for this kernel and for the tcgen05 one.
+extern "C" int rlis_attention_prefill_tile(void) { return RLIS_PREFILL_TILE; }

@@ -44,6 +44,7 @@
 namespace {
 using namespace tc;
 constexpr int TQ = 64;                  // tokens of a CTA
+static_assert(TQ == RLIS_PREFILL_TILE, "the host's tile list is cut for another tile size");
 constexpr int TM = 128;                 // rows of the instruction: two heads x 64 tokens
 constexpr int TN = 128;                 // keys of a block
 constexpr int HD = 64;                  // head size
@@ -487,6 +488,7 @@ int g_pf_splits = 0;      // 0: chosen from the number of tiles and the longest 
 }  // namespace
 
 extern "C" int rlis_attention_prefill_tc_error(void) { return tc::read_error_word(); }
+extern "C" int* rlis_attention_prefill_tc_error_addr(void) { return tc::error_word_addr(); }
 
 // 0: automatic; 1, 2 or 4: the CTAs that share a tile's keys.  For measurements.
 extern "C" void rlis_attention_prefill_tc_set_splits(int splits) { g_pf_splits = splits; }

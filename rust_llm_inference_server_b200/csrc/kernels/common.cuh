@@ -9,6 +9,10 @@
 #define RLIS_F32 0
 #define RLIS_BF16 1
 
+// Tokens of a prompt portion that one CTA of the flash attention kernels takes.  The host cuts the
+// step's tile list to this size (rlis_attention_prefill_tile); both kernels assert that they agree.
+#define RLIS_PREFILL_TILE 64
+
 // Error codes returned by launchers in addition to cudaError_t values (which are positive).
 #define RLIS_ERR_UNSUPPORTED (-1)
 

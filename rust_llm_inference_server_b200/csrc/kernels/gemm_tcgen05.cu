@@ -202,6 +202,7 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
 extern "C" int rlis_gemm_tcgen05_error(void) {
     return tc::read_error_word();
 }
+extern "C" int* rlis_gemm_tcgen05_error_addr(void) { return tc::error_word_addr(); }
 
 // epilogue 0: bf16 y [M, N]; 1: SwiGLU (rows of W interleaved gate/up in blocks of 4), bf16 y [M, N / 2];
 // 2: float32 y [M, N].  K and N must be multiples of 8; pointers 16-byte aligned.

@@ -370,6 +370,7 @@ int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, 
 }  // namespace
 
 extern "C" int rlis_stream_gemm_error(void) { return tc::read_error_word(); }
+extern "C" int* rlis_stream_gemm_error_addr(void) { return tc::error_word_addr(); }
 
 // About how many CTAs a launch is cut into (0: twice the SMs).  For measurements.
 extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }

@@ -173,4 +173,10 @@ static inline int read_error_word() {
     if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }
+// The word's address on the current device (nullptr if the lookup fails).
+static inline int* error_word_addr() {
+    int* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_tc_error) != cudaSuccess) return nullptr;
+    return p;
+}
 }  // namespace tc

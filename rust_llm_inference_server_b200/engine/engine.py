@@ -11,7 +11,16 @@ ids, so the host's work on step k (reading the ids, end-of-sequence checks, sche
 the next step) runs while the GPU computes.  A request that ends on an end-of-sequence token has
 by then one more step in flight; that step's row is dropped when it arrives.  Tokens and their
 order are those of the step-by-step loop (the reference's loop is step by step,
-engine.rs:617-726).
+engine.rs:617-726).  A step is launched ahead only when every request's next token is known to
+have a slot in the cache; when pages are short the loop goes step by step and the scheduler
+preempts as it always does (scheduler.rs:227-246).  Should the plan of a step launched ahead still
+differ from "every request, one token more", the placeholders are taken back and the loop falls
+back to step by step: it never raises with placeholders in place.
+
+Failures.  A step whose packing or launch raises fails the requests of that step only: each ends
+with reason "error", gives back its pages and state slot, and the other requests go on
+(engine.rs:516-528).  The kernels' bounded waits leave an error word on the device; it comes to
+the host with every step's sampled ids, and a step that set it fails its requests the same way.
 """
 
 from __future__ import annotations
@@ -27,7 +36,8 @@ from ..cache import CacheStorage, host, plan_groups, size_groups
 from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, float_bits
-from .runner import ModelRunner, StepEntry
+from ..ops import profile
+from .runner import ModelRunner, StepEntry, StepError
 
 
 class RequestError(ValueError):
@@ -39,9 +49,10 @@ class RequestOutput:
     request_id: int
     prompt_token_ids: list
     token_ids: list
-    finish_reason: str            # "stop" (end-of-sequence token) or "length" (max_tokens)
+    finish_reason: str            # "stop" (end-of-sequence token), "length" (max_tokens) or "error"
     ttft: float                   # seconds from arrival to the first token
     decode_time: float            # seconds from the first token to the last
+    error: str | None = None      # what failed, for finish_reason "error"
 
     @property
     def decode_tokens_per_sec(self) -> float:
@@ -78,6 +89,9 @@ class _Launched:
     pos: list = field(default_factory=list)        # per row: index of the token being sampled
     ahead: bool = False           # launched before its input tokens were known to the host
     ids_dev: object = None        # device ids of all rows, when one kernel sampled them all
+    prep_us: float = 0.0          # host time: scheduling, packing, upload
+    forward_us: float = 0.0       # host time: launching the model
+    sample_us: float = 0.0        # host time: launching the samplers
 
 
 @dataclass
@@ -104,6 +118,18 @@ class EngineStats:
     kv_utilization: float = 0.0
     h2d_bytes: int = 0
     d2h_bytes: int = 0
+    failed_requests: int = 0      # requests ended with reason "error"
+    ahead_fallbacks: int = 0      # steps planned ahead whose placeholders were taken back
+    # host microseconds of the last step and summed over all steps (crates/engine/src/engine.rs:717-724
+    # logs prep_us / forward_us / sample_us per step); `wait` is the time blocked on the sampled ids
+    prep_us: float = 0.0
+    forward_us: float = 0.0
+    sample_us: float = 0.0
+    wait_us: float = 0.0
+    total_prep_us: float = 0.0
+    total_forward_us: float = 0.0
+    total_sample_us: float = 0.0
+    total_wait_us: float = 0.0
 
 
 class LLMEngine:
@@ -157,9 +183,13 @@ class LLMEngine:
         self._pen_host = self._pen_dev = None      # histories of the rows with a repetition penalty
         self._slot = 0
         self._inflight: _Launched | None = None
-        # pages of a window group are handed out as a request grows, so a decode step can run out
-        # of pages and preempt: such models are stepped one by one
-        self._decode_ahead = bool(cfg.decode_ahead) and all(not g.window for g in groups)
+        self._failed: list = []             # outputs of requests that failed with their step
+        # the kernels' error word (bounded waits that ran out) travels with every step's ids
+        self._err_dev = torch.zeros((1,), dtype=torch.int32, device=model.device)
+        self._err_host = pinned((1,))
+        self._decode_ahead = bool(cfg.decode_ahead)
+        # (tests switch this off to reach the fallback of a step ahead whose plan is not the expected one)
+        self._ahead_checks_pages = True
 
     # ---- intake ----
 
@@ -195,15 +225,18 @@ class LLMEngine:
     def step(self) -> list:
         """One turn of the loop: makes sure a step is in flight, launches the one after it where
         that is possible (see the module's head), then reads the first one's tokens.  Returns the
-        requests that finished with them."""
+        requests that ended with them (finished, or failed with their step)."""
         cur, self._inflight = self._inflight, None
         if cur is None:
             cur = self._launch(None)
-            if cur is None:
-                self.last_step = StepEvent(0, 0, False, {}, [])
-                return []
+        if cur is None:
+            ended = self._take_failed()
+            self._publish()
+            self.last_step = StepEvent(0, 0, False, {}, ended)
+            return ended
         nxt = self._launch(cur) if self._may_run_ahead(cur) else None
         new_tokens, finished = self._collect(cur, nxt)
+        finished.extend(self._take_failed())
         self._inflight = nxt
         self._publish()
         self.last_step = StepEvent(cur.n_tokens, cur.n_seqs, cur.all_decode, new_tokens, finished)
@@ -212,7 +245,9 @@ class LLMEngine:
     def _may_run_ahead(self, cur: _Launched) -> bool:
         """The step after `cur` can be launched before `cur`'s tokens are known: every request of
         `cur` gets a token from the device (one kernel for all), goes on after it whatever it is,
-        unless it is an end-of-sequence token, and nobody waits to be admitted."""
+        unless it is an end-of-sequence token, nobody waits to be admitted, and the cache has a
+        slot for every request's next token (else the scheduler would have to preempt, and that
+        is decided step by step)."""
         if not self._decode_ahead or not cur.rows or len(cur.rows) != len(cur.seqs) or cur.ids_dev is None:
             return False
         if self.sched.num_waiting() != 0:
@@ -222,12 +257,21 @@ class LLMEngine:
                 return False
             if s.sampler.params.repetition_penalty != 1.0:      # its history has to be complete on the host
                 return False
+        # the step ahead computes the token that `cur` samples: index len(tokens), so len + 1 slots
+        cache = self.cache
+        for g in range(len(self.groups) if self._ahead_checks_pages else 0):
+            need = sum(cache.pages_needed(s.id, g, len(s.tokens) + 1) for s in cur.rows)
+            if need > cache.num_free_pages(g):
+                return False
         return True
 
     def _launch(self, prev: _Launched | None) -> _Launched | None:
         """Schedules and launches a step and its sampler; waits for nothing.  With `prev`, the step
         is the one after `prev`, whose tokens are still on the device: every request gets a
-        placeholder, and the token ids are copied on the device from `prev`'s sampler output."""
+        placeholder, and the token ids are copied on the device from `prev`'s sampler output.
+        Returns None when nothing was launched: no work, the step's requests failed, or (with
+        `prev`) the plan was not the expected one and the placeholders were taken back."""
+        t0 = time.perf_counter()
         if prev is not None:
             for s in prev.rows:
                 self.sched.append_token(s.id, 0)
@@ -236,7 +280,13 @@ class LLMEngine:
         if prev is not None:
             want = [(s.id, len(s.tokens), len(s.tokens) + 1) for s in prev.rows]
             if preempted or [tuple(x) for x in seqs] != want:
-                raise RuntimeError("decode-ahead: the scheduler did not continue the running requests as they were")
+                # Not "everybody, one token more" after all.  What the plan reserved stays reserved,
+                # a preempted request stays preempted (it recomputes with its real tokens later);
+                # only the placeholders go, and `prev` is collected as a step on its own.
+                for s in prev.rows:
+                    self.sched.drop_last_token(s.id)
+                self.stats.ahead_fallbacks += 1
+                return None
         if not seqs:
             if self.sched.has_work():
                 # no progress is possible: fail everything rather than spin (engine.rs:516-522)
@@ -257,22 +307,49 @@ class LLMEngine:
             entries.append(StepEntry(sid, s.tokens[start:end], start, [end - start - 1] if caught_up else []))
             if caught_up:
                 rows.append(s)
-        st = self.runner.prepare(entries)
-        if prev is not None:
-            st.take_tokens(prev.ids_dev[:len(rows)])
-        logits = self.runner.forward(st)
-        self.stats.h2d_bytes += st.h2d_bytes
-        self.stats.steps += 1
-        self.stats.step_tokens += st.n_tokens
-        self._slot ^= 1
-        out = _Launched(list(seqs), rows, st.n_tokens, st.n_seqs, st.all_decode, logits, self._slot,
-                        ahead=prev is not None)
+        try:
+            st = self.runner.prepare(entries)
+            if prev is not None:
+                st.take_tokens(prev.ids_dev[:len(rows)])
+            t1 = time.perf_counter()
+            logits = self.runner.forward(st)
+            t2 = time.perf_counter()
+            self.stats.h2d_bytes += st.h2d_bytes
+            self.stats.steps += 1
+            self.stats.step_tokens += st.n_tokens
+            self._slot ^= 1
+            out = _Launched(list(seqs), rows, st.n_tokens, st.n_seqs, st.all_decode, logits, self._slot,
+                            ahead=prev is not None)
+            if rows:
+                with profile.span("sampler"):
+                    self._enqueue_sampler(out)
+        except (StepError, ops.KernelError) as err:
+            # only this step's requests fail; the others go on (engine.rs:523-528)
+            self._fail([sid for sid, _, _ in seqs], f"{type(err).__name__}: {err}")
+            return None
+        t3 = time.perf_counter()
+        out.prep_us, out.forward_us, out.sample_us = (t1 - t0) * 1e6, (t2 - t1) * 1e6, (t3 - t2) * 1e6
         if prev is None:
             # (for a step launched ahead this waits until its input tokens are real: `_collect`)
             for sid, start, end in seqs:
                 self.sched.advance(sid, end)
-        if rows:
-            self._enqueue_sampler(out)
+        return out
+
+    def _fail(self, ids: list, why: str) -> None:
+        """Ends the given requests with reason "error": pages and state slots go back, tokens
+        generated so far are returned with the message."""
+        now = time.perf_counter()
+        for sid in ids:
+            s = self.seqs.get(sid)
+            if s is None:
+                continue
+            out = self._finish(s, "error", now)
+            out.error = why
+            self.stats.failed_requests += 1
+            self._failed.append(out)
+
+    def _take_failed(self) -> list:
+        out, self._failed = self._failed, []
         return out
 
     def _enqueue_sampler(self, L: _Launched) -> None:
@@ -305,8 +382,10 @@ class LLMEngine:
             self._fids_host[k][:n].copy_(self._fids_dev[:n], non_blocking=True)
             self.stats.h2d_bytes += n * 20
         if n_plain or n_filt:
+            ops.take_device_errors(self._err_dev)
+            self._err_host[k].copy_(self._err_dev, non_blocking=True)
             self._sampled[k].record()               # on the current stream
-            self.stats.d2h_bytes += n * 4
+            self.stats.d2h_bytes += n * 4 + 4
         if n_plain == n:
             L.ids_dev = self._ids_dev
         elif n_filt == n:
@@ -348,8 +427,20 @@ class LLMEngine:
         step launched after it with placeholders, which now get their values."""
         new_tokens, finished = {}, []
         rows, n, k = L.rows, len(L.rows), L.slot
+        st = self.stats
+        st.prep_us, st.forward_us, st.sample_us, st.wait_us = L.prep_us, L.forward_us, L.sample_us, 0.0
         if rows:
+            t0 = time.perf_counter()
             self._sampled[k].synchronize()
+            st.wait_us = (time.perf_counter() - t0) * 1e6
+            code = self._device_error(k)
+            if code:
+                # a bounded wait ran out inside a kernel of this step (or of the one launched after
+                # it): what they computed is not to be trusted
+                ids = [s.id for s in rows] + ([s.id for s in nxt.rows] if nxt is not None else [])
+                self._fail(ids, f"a bounded wait of a kernel ran out on the device (code {code}); "
+                                "the step's results were dropped")
+                return new_tokens, finished
             a, b = self._ids_host[k][:n].tolist(), self._fids_host[k][:n].tolist()
             tokens = [a[i] if L.plain[i] is not None else b[i] for i in range(n)]
             now = time.perf_counter()
@@ -360,12 +451,20 @@ class LLMEngine:
                 out = self._accept(s, int(tok), now, placeholder=nxt is not None)
                 if out is not None:
                     finished.append(out)
+        st.total_prep_us += st.prep_us
+        st.total_forward_us += st.forward_us
+        st.total_sample_us += st.sample_us
+        st.total_wait_us += st.wait_us
         if nxt is not None:
             # its input tokens are real now: pages they fill may enter the prefix registry
             for sid, start, end in nxt.seqs:
                 if sid in self.seqs:
                     self.sched.advance(sid, end)
         return new_tokens, finished
+
+    def _device_error(self, slot: int) -> int:
+        """The kernels' error word as it came to the host with the ids of the step in `slot`."""
+        return int(self._err_host[slot][0])
 
     def _accept(self, s: _Sequence, token: int, now: float, placeholder: bool = False):
         """Records a sampled token; finishes the request on end-of-sequence (not appended) unless

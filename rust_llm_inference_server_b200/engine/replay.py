@@ -26,7 +26,7 @@ from ..models import load_model
 from .runner import ModelRunner, StepEntry
 
 REPLAY_PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 64
 
 
 class ReplaySession:
@@ -36,6 +36,8 @@ class ReplaySession:
             raise RuntimeError("trace replay needs a CUDA device; there is no CPU path")
         self.model = load_model(model_dir, dtype, device)
         groups = plan_groups(self.model.cache_slot_specs, page_size)
+        if page_size <= 0:
+            raise ValueError(f"page size must be positive, got {page_size}")
         # The pool holds exactly `max_tokens` tokens, so pages are used again as requests end.
         n_pages = max(1, (int(max_tokens) + page_size - 1) // page_size)
         for g in groups:

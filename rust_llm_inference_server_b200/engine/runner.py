@@ -16,6 +16,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..ops import profile
 
 
 class StepError(ValueError):
@@ -60,7 +61,7 @@ class StepContext:
         self.n_prefill_tokens = 0
         self.prefill_rows = None                  # int32: rows of the tokens of longer entries
         self.n_prefill_tiles = 0
-        self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token), 64 tokens a tile
+        self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token of the tile)
         self.n_wanted = 0                         # rows whose logits are asked for
         self._views = None
         self._token_region = None
@@ -81,7 +82,6 @@ class StepContext:
 
 
 class ModelRunner:
-    PREFILL_TILE = 64           # query tokens per CTA of the prefill attention kernel
     GRAPH_AFTER_STEPS = 2       # eager steps of a decode shape before its graph is captured
 
     def __init__(self, model, cache_manager, storage, max_seq_len: int):
@@ -94,6 +94,8 @@ class ModelRunner:
         self.max_blocks = max(1, max((self.max_seq_len + g.page_size - 1) // g.page_size for g in self.groups)) \
             if self.groups else 1
         self._caches = [storage.layer_cache(c) for c in range(len(model.cache_slot_specs))]
+        # tokens of a portion that one CTA of the mixers' prompt kernels takes (None: no tile list)
+        self.prefill_tile = model.prefill_tile
         self._states = storage.states
         self._ws: dict[str, torch.Tensor] = {}
         self._meta_host = None
@@ -186,7 +188,8 @@ class ModelRunner:
                 pf_rows.extend(range(k, k + n))
             k += n
         Bd, Tp = len(dec_rows), len(pf_rows)
-        pf_tiles = [(b, t0) for b, n in enumerate(lens) if n > 1 for t0 in range(0, n, self.PREFILL_TILE)]
+        pf_tiles = [(b, t0) for b, n in enumerate(lens) if n > 1 for t0 in range(0, n, self.prefill_tile)] \
+            if self.prefill_tile else []
         # the tiles with the most keys to read first: the GPU hands out CTAs in this order, and the
         # long ones must not be the last to start
         pf_tiles.sort(key=lambda bt: -(starts[bt[0]] + bt[1]))
@@ -281,7 +284,7 @@ class ModelRunner:
     def _graph_key(self, st: StepContext):
         """Decode-only steps of a model whose parts read nothing from the host run from a captured
         graph: the launch-bound inner loop of generation (about ten kernels a layer)."""
-        if not (self.use_graphs and st.all_decode and self.model.graph_safe):
+        if not (self.use_graphs and st.all_decode and self.model.graph_safe) or profile.enabled:
             return None
         W = st.n_wanted
         # the parts say what else of the step reaches a launch configuration (the number of pieces

@@ -9,8 +9,8 @@ from __future__ import annotations
 
 from ..config.model_config import LlamaConfig
 from ..config.registry import register_architecture
-from ..parts.spec import (GQAAttentionSpec, LayerCall, LayerSpec, ModelSpec, RMSNormSpec, RopeSpec,
-                          SwiGLUSpec)
+from ..parts.spec import (EmbeddingSpec, GQAAttentionSpec, LayerCall, LayerSpec, LMHeadSpec, ModelSpec,
+                          RMSNormSpec, RopeSpec, SwiGLUSpec)
 
 
 def describe_llama(cfg: LlamaConfig) -> ModelSpec:
@@ -31,10 +31,13 @@ def describe_llama(cfg: LlamaConfig) -> ModelSpec:
         ))
     embed = "model.embed_tokens.weight"
     return ModelSpec(
-        vocab_size=cfg.vocab_size, hidden=H, embedding=embed, layers=tuple(layers),
+        vocab_size=cfg.vocab_size, hidden=H,
+        # the table's rows as they are (no scaling by sqrt(hidden), llama.rs:256-262)
+        embedding=EmbeddingSpec(cfg.vocab_size, H, embed), layers=tuple(layers),
         order=tuple(LayerCall(i, i) for i in range(cfg.num_hidden_layers)),
         final_norm=RMSNormSpec(H, cfg.rms_norm_eps, "model.norm.weight"),
-        lm_head=embed if cfg.tie_word_embeddings else "lm_head.weight",
+        # the product alone, in float32 (no logit scale, no cap, llama.rs:279-285)
+        lm_head=LMHeadSpec(cfg.vocab_size, H, embed if cfg.tie_word_embeddings else "lm_head.weight"),
         max_positions=cfg.max_position_embeddings,
         # A tied checkpoint that still stores lm_head.weight is read without it
         # (crates/model/src/llama.rs:152-156).

@@ -8,11 +8,10 @@ from __future__ import annotations
 
 import torch
 
-from .. import ops
 from ..config.model_config import read_config_json
 from ..config.registry import lookup_architecture
-from ..parts.base import Part, build_block, build_norm
-from ..parts.spec import ModelSpec
+from ..parts.base import Part, build_block, build_embedding, build_lm_head, build_norm
+from ..parts.spec import EmbeddingSpec, LMHeadSpec, ModelSpec
 from ..weights.loader import PlacedSource, check_checkpoint
 from ..weights.safetensors_io import Checkpoint, open_model_dir
 
@@ -36,19 +35,39 @@ class Model:
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
+        # a spec may name the two ends by their tensors alone: plain lookup, plain product
+        emb = spec.embedding if not isinstance(spec.embedding, str) \
+            else EmbeddingSpec(spec.vocab_size, spec.hidden, spec.embedding)
+        head = spec.lm_head if not isinstance(spec.lm_head, str) \
+            else LMHeadSpec(spec.vocab_size, spec.hidden, spec.lm_head)
+        self.embedding = build_embedding(emb, dtype, self.device)
         self.blocks = [build_block(ls, dtype, self.device) for ls in spec.layers]
         self.final_norm = build_norm(spec.final_norm, dtype, self.device)
+        self.lm_head = build_lm_head(head, dtype, self.device)
         self.calls = tuple(spec.order)
-        self.embed = None
-        self.lm_head = None
         self._plan_caches()
         # parts whose launch configuration depends on more than the step's shape
-        self._variant_parts = [p for blk in self.blocks for p in blk.parts()
+        self._variant_parts = [p for p in self.parts()
                                if getattr(type(p), "launch_variant", Part.launch_variant) is not Part.launch_variant]
         # whether a step of this model can be captured in a CUDA graph: every part launches the
         # same kernels on the same device buffers whatever the host-side lists of the step hold
-        self.graph_safe = all(getattr(p, "graph_safe", False) for blk in self.blocks for p in blk.parts()) \
-            and getattr(self.final_norm, "graph_safe", False)
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.parts())
+
+    @property
+    def prefill_tile(self):
+        """The tile of prompt tokens the mixers' kernels want listed in a step (None: none does)."""
+        tiles = {m.prefill_tile for m in (blk.mixer for blk in self.blocks) if getattr(m, "prefill_tile", None)}
+        if len(tiles) > 1:
+            raise ValueError(f"the mixers ask for prompt tiles of different sizes: {sorted(tiles)}")
+        return tiles.pop() if tiles else None
+
+    def parts(self):
+        """Every part of the model, ends included."""
+        yield self.embedding
+        for blk in self.blocks:
+            yield from blk.parts()
+        yield self.final_norm
+        yield self.lm_head
 
     def launch_variant(self, step) -> tuple:
         """What of a decode step, beyond its shape, reaches a launch configuration: steps with the
@@ -85,27 +104,19 @@ class Model:
     # ---- weights ----
 
     def tensors(self) -> dict:
-        out = {self.spec.embedding: (self.spec.vocab_size, self.spec.hidden),
-               self.spec.lm_head: (self.spec.vocab_size, self.spec.hidden)}
-        for blk in self.blocks:
-            for part in blk.parts():
-                for name, shape in part.tensors().items():
-                    if name in out and tuple(out[name]) != tuple(shape):
-                        raise ValueError(f"tensor {name} is expected with shapes {out[name]} and {shape}")
-                    out[name] = tuple(shape)
-        out.update(self.final_norm.tensors())
+        out: dict = {}
+        for part in self.parts():
+            for name, shape in part.tensors().items():
+                if name in out and tuple(out[name]) != tuple(shape):
+                    raise ValueError(f"tensor {name} is expected with shapes {out[name]} and {shape}")
+                out[name] = tuple(shape)
         return out
 
     def load(self, ckpt: Checkpoint) -> None:
         check_checkpoint(self.tensors(), ckpt, self.spec.ignorable)
         src = PlacedSource(ckpt, self.dtype, self.device)
-        self.embed = src.get(self.spec.embedding).contiguous()
-        self.lm_head = self.embed if self.spec.lm_head == self.spec.embedding \
-            else src.get(self.spec.lm_head).contiguous()
-        for blk in self.blocks:
-            for part in blk.parts():
-                part.load(src)
-        self.final_norm.load(src)
+        for part in self.parts():
+            part.load(src)
 
     # ---- forward ----
 
@@ -114,7 +125,7 @@ class Model:
         residual stream and the last pending delta; `logits` finishes chosen rows."""
         T = step.n_tokens
         resid = step.buffer("resid", (T, self.spec.hidden), torch.float32)
-        ops.embedding(step.token_ids, self.embed, resid)
+        self.embedding.forward(step.token_ids, resid, step)
         delta = None
         for ci, call in enumerate(self.calls):
             blk = self.blocks[call.layer]
@@ -131,7 +142,7 @@ class Model:
         """Final norm and LM head on the rows in `rows` (int32 indices into the step's tokens):
         float32 logits [len(rows), vocab] (crates/model/src/llama.rs:272-285)."""
         h = self.final_norm.forward_rows(resid, delta, step, rows)
-        return ops.linear(h, self.lm_head, out_dtype=torch.float32)
+        return self.lm_head.forward(h, step)
 
 
 def build_model(config_json: dict, dtype, device="cuda") -> Model:

@@ -11,11 +11,11 @@ no reduced-precision matrix mode can enter.
 from __future__ import annotations
 
 import functools
-import os
 
 import torch
 
-from .library import KernelError, check, lib
+from . import library
+from .library import KernelError, check, debug_set, lib
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -25,10 +25,10 @@ launch_count = 0
 
 
 def set_programmatic_launch(on: bool) -> None:
-    """Launch kernels with the programmatic-serialization attribute (default off; also
-    RLIS_PDL=1): the next kernel's CTAs are launched while the current one drains; see
-    csrc/kernels/common.cuh."""
-    lib().rlis_set_pdl(1 if on else 0)
+    """Whether kernels are launched with the programmatic-serialization attribute (on unless
+    switched off, here or by RLIS_DEBUG=pdl=0): the next kernel's CTAs start their prologue while
+    the current kernel drains; see csrc/kernels/common.cuh."""
+    debug_set("pdl", 1 if on else 0)
 
 
 def _code(dtype) -> int:
@@ -61,22 +61,51 @@ def _req(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
             raise KernelError(f"{name}: expected shape {shape}, got {tuple(t.shape)}")
 
 
-def _count() -> None:
+# The same by kernel, for tests that have to know which kernel a step went through:
+# {"stream_gemm.sink": 12, "attention_decode_qkv.mma.tma": 4, ...}.
+launches_by_kernel: dict = {}
+
+
+def _count(name: str) -> None:
     global launch_count
     launch_count += 1
+    launches_by_kernel[name] = launches_by_kernel.get(name, 0) + 1
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = table[ids[t], :] widened to float32.  ids int32 [T]; out float32 [T, H]."""
+def _decode_variant() -> str:
+    """Which decode-attention kernel the launcher just chose."""
+    v = lib().rlis_attention_decode_last_variant()
+    if not v & 1:
+        return ".cuda_core"
+    return ".mma" + (".tma" if v & 2 else "") + (".cluster" if v & 4 else "")
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] widened to float32 (times `scale` if given).  ids int32 [T];
+    out float32 [T, H]."""
     V, H = table.shape
     T = ids.shape[0]
     _req(ids, "ids", torch.int32, (T,))
     _req(table, "table")
     _req(out, "out", torch.float32, (T, H))
     check(lib().rlis_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), T, H, V,
-                               _code(table.dtype), _stream()), "embedding")
-    _count()
+                               1.0 if scale is None else float(scale), _code(table.dtype), _stream()), "embedding")
+    _count("embedding")
     return out
+
+
+def logit_transform(logits: torch.Tensor, scale: float | None, soft_cap: float | None) -> torch.Tensor:
+    """In place on float32 logits [R, V]: x <- x * scale, then x <- cap * tanh(x / cap) (each only
+    where given)."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise KernelError("logit_transform: logits must be float32 CUDA rows with unit stride")
+    if soft_cap is not None and not soft_cap > 0:
+        raise KernelError(f"logit_transform: the cap must be positive, got {soft_cap}")
+    check(lib().rlis_logit_transform(logits.data_ptr(), R, V, logits.stride(0), 1.0 if scale is None else float(scale),
+                                     0.0 if soft_cap is None else float(soft_cap), _stream()), "logit_transform")
+    _count("logit_transform")
+    return logits
 
 
 def rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -100,7 +129,7 @@ def rmsnorm(resid: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Te
                              weight.data_ptr(), out.data_ptr(),
                              rows.data_ptr() if rows is not None else None, n_out, H, float(eps),
                              _code(out.dtype), _stream()), "rmsnorm")
-    _count()
+    _count("rmsnorm" if rows is None else "rmsnorm.rows")
     return out
 
 
@@ -114,7 +143,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> tor
     _req(out, "out", gate_up.dtype, (T, I2 // 2))
     check(lib().rlis_swiglu(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, int(interleave),
                             _code(out.dtype), _stream()), "swiglu")
-    _count()
+    _count("swiglu")
     return out
 
 
@@ -129,11 +158,11 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     _req(out, "out", torch.float32, (M, N))
     check(lib().rlis_gemm_f32_nt(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _stream()),
           "gemm_f32")
-    _count()
+    _count("gemm_f32")
     return out
 
 
-FUSE_NORMS = os.environ.get("RLIS_FUSE_NORMS", "1") != "0"     # for measurements: 0 runs every norm as a kernel
+FUSE_NORMS = True          # debug switch "fuse_norms": 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
 DECODE_GEMM_ROWS = 16     # up to this many rows `linear` uses it; longer batches go to the library GEMM
 
@@ -181,7 +210,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
         out = torch.empty((M, N // 2 if swiglu4 else N), dtype=out_dtype, device=x.device)
         check(lib().rlis_stream_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
                                           1 if swiglu4 else 0, _stream()), "stream_gemm")
-        _count()
+        _count("stream_gemm.swiglu" if swiglu4 else "stream_gemm")
         return out
     in_p, n_p, dim, eps = 0, 0, 0, 0.0
     if scaled is not None:
@@ -197,7 +226,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
         check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, _code(out_dtype),
                                            1 if swiglu4 else 0, in_p, n_p, dim, eps, 0, 0, 0, 0, _stream()),
               "stream_gemm")
-        _count()
+        _count("stream_gemm.scaled.swiglu" if swiglu4 else "stream_gemm.scaled")
         return out
     if swiglu4 or M > DECODE_GEMM_ROWS:
         raise KernelError(f"stream_gemm: a sink takes a plain product of up to {DECODE_GEMM_ROWS} rows")
@@ -208,7 +237,7 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
     check(lib().rlis_stream_gemm_fused(x.data_ptr(), w.data_ptr(), 0, M, N, K, _code(torch.bfloat16), 2, 0, 0, 0, 0.0,
                                        sink.resid.data_ptr(), sink.weight.data_ptr(), xn.data_ptr(),
                                        partials.data_ptr(), _stream()), "stream_gemm")
-    _count()
+    _count("stream_gemm.sink")
     return ScaledRows(xn, partials, N, sink.eps)
 
 
@@ -228,7 +257,18 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> t
                       device=x.device)
     check(lib().rlis_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, code, _stream()),
           "gemm_tcgen05")
-    _count()
+    _count("gemm_tcgen05." + epilogue)
+    return out
+
+
+def take_device_errors(out: torch.Tensor) -> torch.Tensor:
+    """Reads and clears, in stream order, the error words of the kernels' bounded waits and leaves
+    their union in `out` (int32 [1] on the device): non-zero when a wait ran out in a kernel launched
+    before this call and after the last one.  No synchronisation; copy `out` to the host with
+    whatever else the step brings back."""
+    _req(out, "out", torch.int32, (1,))
+    check(lib().rlis_take_errors(out.data_ptr(), _stream()), "take_errors")
+    _count("take_errors")
     return out
 
 
@@ -295,7 +335,7 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | N
         positions.data_ptr(), slots.data_ptr() if slots is not None else None,
         inv_freq.data_ptr() if inv_freq is not None else None,
         T, n_heads, n_kv_heads, head_dim, page_size, _code(qkv.dtype), _stream()), "rope_cache")
-    _count()
+    _count("rope_cache")
     return q_out
 
 
@@ -328,19 +368,31 @@ def attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         block_tables.shape[1], T if token_rows is None else token_rows.shape[0], n_heads,
         n_kv_heads, head_dim, page_size, float(scale), int(window), _code(q.dtype), _stream()),
         "attention_generic")
-    _count()
+    _count("attention_generic")
     return out
 
 
-NUM_SMS = 148
-DECODE_CLUSTER_MAX_CTAS = 4 * 148     # larger grids merge their pieces through global memory instead
 DECODE_MIN_KEYS_PER_SPLIT = 128
 
 
+@functools.lru_cache(maxsize=None)
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device (what the launchers ask the runtime for)."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device; there is no CPU path")
+    return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+
+
+def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int, sms: int | None = None) -> int:
+    """How many pieces the context is cut into for decode attention on a device of `sms`
+    multiprocessors (None: the current device); see `_decode_splits`."""
+    return _decode_splits(n_decode, n_kv_heads, max_ctx, num_sms() if sms is None else int(sms))
+
+
 @functools.lru_cache(maxsize=4096)
-def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
-    """How many pieces the context is cut into for decode attention (role of `split_plan`,
-    crates/model/src/paged_attention.rs:21-36, re-tuned by measurement on 148 SMs).  Few requests:
+def _decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int, sms: int) -> int:
+    """Role of `split_plan`, crates/model/src/paged_attention.rs:21-36, re-tuned by measurement
+    (on 148 multiprocessors, which the numbers below are for).  Few requests:
     enough CTAs (kv heads x requests x pieces) to fill the SMs about twice, each piece at least
     128 keys long.  From 64 (request, kv head) pairs on, pieces of at least 512 keys and no more
     than about 384 CTAs; from 256 pairs on, one piece at every context: the pairs fill the SMs by
@@ -349,13 +401,14 @@ def decode_splits(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
     merged inside a thread-block cluster, and clusters of 2, 4 and 8 are the sizes that schedule
     well (batch 8, context 4096: 17.4 us with 4 pieces, 29.2 with 5)."""
     groups = max(1, n_decode * n_kv_heads)
-    want = -(-2 * NUM_SMS // groups)
+    cluster_max_ctas = 4 * sms     # larger grids merge their pieces through global memory instead
+    want = -(-2 * sms // groups)
     min_keys = DECODE_MIN_KEYS_PER_SPLIT
     if groups >= 64:
         want = min(want, max(1, 384 // groups))
         min_keys = 512
     want = max(1, min(want, max_ctx // min_keys, 32))
-    if want > 1 and groups * min(want, 8) <= DECODE_CLUSTER_MAX_CTAS:
+    if want > 1 and groups * min(want, 8) <= cluster_max_ctas:
         # merged inside a cluster: 2, 4 or 8 pieces; with few requests 8, until a piece gets long
         # (batch 1, context 4096: 6.7 us with 8 pieces in a cluster, 12.6 us with 32 and tickets)
         pieces = 1 << (min(want, 8).bit_length() - 1)
@@ -392,7 +445,7 @@ def attention_decode(q, k_cache, v_cache, out, dec_rows, dec_seqs, ctx_lens, blo
         ctx_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n, n_heads,
         n_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), int(splits),
         _code(q.dtype), _stream()), "attention_decode")
-    _count()
+    _count("attention_decode" + _decode_variant())
     return out
 
 
@@ -433,19 +486,35 @@ def attention_decode_from_qkv(qkv, k_cache, v_cache, out, step, group: int, inv_
         n_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale), int(window), int(splits),
         _code(qkv.dtype), _stream()),
         "attention_decode_qkv")
-    _count()
+    _count("attention_decode_qkv" + _decode_variant())
     return out
 
 
-PREFILL_TCGEN05 = True     # False: the mma.sync kernel for every size (measurements, tests of that kernel)
+@functools.lru_cache(maxsize=None)
+def prefill_tile() -> int:
+    """Tokens of a portion that one CTA of the flash kernels for prompt portions takes; the step's
+    tile list (`attention_prefill`'s `tiles`) is cut to this size."""
+    return int(lib().rlis_attention_prefill_tile())
+
+
+PREFILL_TCGEN05 = True     # debug switch "prefill_tcgen05": 0 takes the mma.sync kernel for every size
+
+
+def _set_flag(name):
+    def setter(value):
+        globals()[name] = bool(value)
+    return setter
+
+
+library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"))
 
 
 def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,
                       n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, scale: float,
                       window: int = 0, max_ctx: int = 0) -> torch.Tensor:
     """Causal flash attention of portions of prompts over the paged cache (bfloat16, head sizes 64
-    and 128).  tiles int32 [n, 2] = (batch entry, first token of the 64-token tile within the
-    entry's portion); cu_seqlens int32 [B + 1] = rows of the entries' first tokens.  max_ctx: the
+    and 128).  tiles int32 [n, 2] = (batch entry, first token of the tile within the entry's
+    portion; a tile is `prefill_tile()` tokens); cu_seqlens int32 [B + 1] = rows of the entries' first tokens.  max_ctx: the
     longest context of the step if known (with few tiles and long contexts several CTAs then
     share a tile's keys)."""
     _req(q, "q", torch.bfloat16, (None, n_heads * head_dim))
@@ -465,14 +534,14 @@ def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, blo
             tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),
             block_tables.shape[1], q.shape[0], k_cache.shape[0], n_heads, n_kv_heads, head_dim, page_size,
             float(scale), int(window), _code(q.dtype), int(max_ctx), _stream()), "attention_prefill_tc")
-        _count()
+        _count("attention_prefill.tcgen05")
         return out
     check(lib().rlis_attention_prefill(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
         tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),
         block_tables.shape[1], n_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
         _code(q.dtype), _stream()), "attention_prefill")
-    _count()
+    _count("attention_prefill.mma")
     return out
 
 
@@ -525,7 +594,7 @@ def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | 
     _req(out, "out", torch.int32, (R,))
     check(lib().rlis_sample_rows(logits.data_ptr(), params.data_ptr(), out.data_ptr(), R, V,
                                  logits.stride(0), _stream()), "sample_rows")
-    _count()
+    _count("sample_rows")
     return out
 
 
@@ -544,7 +613,7 @@ def repetition_penalty(logits: torch.Tensor, rows: torch.Tensor, history: torch.
     _req(penalties, "penalties", torch.float32, (n,))
     check(lib().rlis_repetition_penalty(logits.data_ptr(), rows.data_ptr(), history.data_ptr(), offsets.data_ptr(),
                                         penalties.data_ptr(), n, V, logits.stride(0), _stream()), "repetition_penalty")
-    _count()
+    _count("repetition_penalty")
     return logits
 
 
@@ -561,7 +630,7 @@ def sample_filtered(logits: torch.Tensor, params: torch.Tensor, out: torch.Tenso
     _req(out, "out", torch.int32, (R,))
     check(lib().rlis_sample_filtered(logits.data_ptr(), params.data_ptr(), out.data_ptr(), R, V,
                                      logits.stride(0), _stream()), "sample_filtered")
-    _count()
+    _count("sample_filtered")
     return out
 
 
@@ -574,5 +643,5 @@ def nll_rows(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
     out = torch.empty((R,), dtype=torch.float32, device=logits.device)
     check(lib().rlis_nll_rows(logits.data_ptr(), targets.data_ptr(), out.data_ptr(), R, V,
                               logits.stride(0), _stream()), "nll_rows")
-    _count()
+    _count("nll_rows")
     return out

@@ -21,7 +21,9 @@ LL = c_longlong
 
 # name -> argument types (the stream is always last)
 SIGNATURES = {
-    "rlis_embedding": [P, P, P, I, I, I, I, P],
+    "rlis_embedding": [P, P, P, I, I, I, F, I, P],
+    "rlis_logit_transform": [P, I, I, LL, F, F, P],
+    "rlis_attention_prefill_tile": [],
     "rlis_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
     "rlis_swiglu": [P, P, I, I, I, I, P],
     "rlis_gemm_f32_nt": [P, P, P, I, I, I, P],
@@ -40,6 +42,8 @@ SIGNATURES = {
     "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
     "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, P],
+    "rlis_take_errors": [P, P],
+    "rlis_attention_decode_last_variant": [],
 }
 
 OPTIONAL_SIGNATURES: dict = {}
@@ -47,6 +51,22 @@ OPTIONAL_SIGNATURES: dict = {}
 
 class KernelError(RuntimeError):
     pass
+
+
+# Switches for measurements and tests; nothing in the engine sets one.  In the library
+# (csrc/kernels/runtime_switches.cu): pdl, stream_ctas, decode_stages, decode_cluster, decode_tma,
+# prefill_splits, filtered_cluster.  In Python (ops/__init__.py): fuse_norms, prefill_tcgen05.
+# `RLIS_DEBUG=name=value,name=value` in the environment sets them when the library is loaded.
+PYTHON_SWITCHES: dict = {}
+
+
+def debug_set(name: str, value: int) -> None:
+    """Holds one of the kernels' own choices fixed (see the list above)."""
+    if name in PYTHON_SWITCHES:
+        PYTHON_SWITCHES[name](int(value))
+        return
+    if lib().rlis_debug_set(name.encode(), int(value)) != 0:
+        raise KernelError(f"no debug switch {name!r}")
 
 
 def lib():
@@ -64,35 +84,17 @@ def lib():
                 raise KernelError(f"kernel library {path} lacks symbol {name}") from e
             fn.argtypes = args
             fn.restype = c_int
-        handle.rlis_gemm_tcgen05_error.argtypes = []
-        handle.rlis_gemm_tcgen05_error.restype = c_int
-        handle.rlis_attention_prefill_tc_set_splits.argtypes = [c_int]
-        handle.rlis_attention_prefill_tc_set_splits.restype = None
-        handle.rlis_attention_prefill_tc_error.argtypes = []
-        handle.rlis_attention_prefill_tc_error.restype = c_int
-        handle.rlis_stream_gemm_error.argtypes = []
-        handle.rlis_stream_gemm_error.restype = c_int
-        handle.rlis_stream_gemm_set_target.argtypes = [c_int]
-        handle.rlis_stream_gemm_set_target.restype = None
-        handle.rlis_attention_decode_set_stages.argtypes = [c_int]
-        handle.rlis_attention_decode_set_stages.restype = None
-        handle.rlis_sample_filtered_set_cluster.argtypes = [c_int]
-        handle.rlis_sample_filtered_set_cluster.restype = None
-        handle.rlis_attention_decode_set_tma.argtypes = [c_int]
-        handle.rlis_attention_decode_set_tma.restype = None
-        handle.rlis_attention_decode_error.argtypes = []
-        handle.rlis_attention_decode_error.restype = c_int
-        handle.rlis_attention_decode_set_cluster.argtypes = [c_int]
-        handle.rlis_attention_decode_set_cluster.restype = None
-        handle.rlis_set_pdl.argtypes = [c_int]
-        handle.rlis_set_pdl.restype = None
-        if os.environ.get("RLIS_PDL", "1") == "0":      # programmatic dependent launch is on unless switched off
-            handle.rlis_set_pdl(0)
-        if os.environ.get("RLIS_STREAM_CTAS"):           # for measurements: CTAs a streaming product is cut into
-            handle.rlis_stream_gemm_set_target(int(os.environ["RLIS_STREAM_CTAS"]))
-        if os.environ.get("RLIS_DECODE_STAGES"):         # for measurements: stages of keys in decode attention
-            handle.rlis_attention_decode_set_stages(int(os.environ["RLIS_DECODE_STAGES"]))
+        for name in ("rlis_gemm_tcgen05_error", "rlis_stream_gemm_error", "rlis_attention_prefill_tc_error",
+                     "rlis_attention_decode_error"):
+            fn = getattr(handle, name)
+            fn.argtypes = []
+            fn.restype = c_int
+        handle.rlis_debug_set.argtypes = [ctypes.c_char_p, c_int]
+        handle.rlis_debug_set.restype = c_int
         _lib = handle
+        for item in filter(None, os.environ.get("RLIS_DEBUG", "").split(",")):
+            name, _, value = item.partition("=")
+            debug_set(name.strip(), int(value))
     return _lib
 
 

@@ -7,6 +7,7 @@ import math
 import torch
 
 from .. import ops
+from ..ops.profile import span
 from .base import KVCacheSpec, Mixer, build_position, register_mixer
 
 
@@ -50,6 +51,11 @@ class GQAAttention(Mixer):
         s = self.spec
         return KVCacheSpec(s.n_kv_heads, s.head_dim, s.window)
 
+    @property
+    def prefill_tile(self):
+        # the flash kernels for prompt portions take one tile of this many tokens a CTA
+        return ops.prefill_tile() if self.dtype == torch.bfloat16 and self.spec.head_dim in (64, 128) else None
+
     def launch_variant(self, step):
         # decode attention cuts the context into pieces by the longest context of the step
         s = self.spec
@@ -62,23 +68,29 @@ class GQAAttention(Mixer):
     def forward(self, x, step, cache, state, writes_cache=True, sink=None):
         s = self.spec
         T = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv)
+        with span("qkv proj"):
+            qkv = ops.linear(x, self.w_qkv)
         o = step.buffer("attn_o", (T, s.n_heads * s.head_dim), self.dtype)
         if step.all_decode and ops.decode_attention_takes_qkv(qkv.dtype, s.n_heads, s.n_kv_heads, s.head_dim):
             table = self.position.rotate_half_table()
             if table is not NotImplemented:
                 # a step of single tokens: the attention kernel rotates q and the newest key and
                 # stores that key itself, one kernel fewer a layer
-                ops.attention_decode_from_qkv(qkv, cache.k, cache.v, o, step, cache.group, table, writes_cache,
-                                              s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size,
-                                              self.scale, self.window)
-                return ops.linear(o, self.w_o, sink=sink)
+                with span("rope + kv write + attention"):
+                    ops.attention_decode_from_qkv(qkv, cache.k, cache.v, o, step, cache.group, table, writes_cache,
+                                                  s.n_heads, s.n_kv_heads, s.head_dim, cache.page_size,
+                                                  self.scale, self.window)
+                with span("o proj"):
+                    return ops.linear(o, self.w_o, sink=sink)
         q = step.buffer("attn_q", (T, s.n_heads * s.head_dim), self.dtype)
-        self.position.encode_and_store(qkv, q, cache, step, s.n_heads, s.n_kv_heads, s.head_dim,
-                                       store=writes_cache)
-        ops.attention(q, cache.k, cache.v, o, step, cache.group, s.n_heads, s.n_kv_heads,
-                      s.head_dim, cache.page_size, self.scale, self.window)
-        return ops.linear(o, self.w_o, sink=sink)
+        with span("rope + kv write"):
+            self.position.encode_and_store(qkv, q, cache, step, s.n_heads, s.n_kv_heads, s.head_dim,
+                                           store=writes_cache)
+        with span("attention"):
+            ops.attention(q, cache.k, cache.v, o, step, cache.group, s.n_heads, s.n_kv_heads,
+                          s.head_dim, cache.page_size, self.scale, self.window)
+        with span("o proj"):
+            return ops.linear(o, self.w_o, sink=sink)
 
 
 register_mixer("gqa_attention", GQAAttention)

@@ -18,9 +18,12 @@ class TensorSource:
     role "matrix": a matrix-product operand, in the compute type (bfloat16 or float32);
     role "vector": a norm weight or other small float table, widened exactly to float32;
     role "index":  an integer table, as int32;
-    role "stored": whatever the checkpoint holds, unchanged (32-bit stays 32-bit)."""
+    role "stored": whatever the checkpoint holds, unchanged (32-bit stays 32-bit).
 
-    def get(self, name: str, role: str = "matrix") -> torch.Tensor:  # pragma: no cover
+    `share=True`: parts that ask for the same tensor in the same role get one copy on the device
+    (tied embedding and LM head)."""
+
+    def get(self, name: str, role: str = "matrix", share: bool = False) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
 
@@ -76,9 +79,30 @@ class LayerCache:
     page_size: int
 
 
+class TokenEmbedding(Part):
+    """Starts the residual stream: `forward(token_ids, out, step)` fills `out`, float32
+    [tokens, hidden], from int32 ids on the device."""
+
+    def forward(self, token_ids: torch.Tensor, out: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class LogitsHead(Part):
+    """Ends it: `forward(h, step)` takes the normed rows whose logits are wanted, [rows, hidden] in
+    the compute type, and returns float32 logits [rows, vocab]."""
+
+    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Mixer(Part):
     """Token mixing over a request's earlier tokens.  `forward` gets the normed activations
     [T, hidden] of all tokens of the step and returns [T, hidden] in the same element type."""
+
+    # Tokens of a request that one CTA of the mixer's kernel for prompt portions takes; the step
+    # function then lists every portion of the step in tiles of that many tokens
+    # (`step.prefill_tiles`).  None: the mixer needs no such list.
+    prefill_tile: Optional[int] = None
 
     def cache_spec(self) -> Optional[KVCacheSpec]:
         return None
@@ -135,6 +159,8 @@ _FEED_FORWARDS: dict[str, Callable] = {}
 _NORMS: dict[str, Callable] = {}
 _POSITIONS: dict[str, Callable] = {}
 _ARRANGEMENTS: dict[str, Callable] = {}
+_EMBEDDINGS: dict[str, Callable] = {}
+_LM_HEADS: dict[str, Callable] = {}
 
 
 def _register(table: dict, what: str):
@@ -150,6 +176,8 @@ register_feed_forward = _register(_FEED_FORWARDS, "feed-forward")
 register_norm = _register(_NORMS, "norm")
 register_position = _register(_POSITIONS, "position encoding")
 register_arrangement = _register(_ARRANGEMENTS, "block arrangement")
+register_embedding = _register(_EMBEDDINGS, "embedding")
+register_lm_head = _register(_LM_HEADS, "LM head")
 
 
 def _build(table: dict, what: str, spec, dtype, device):
@@ -173,6 +201,14 @@ def build_norm(spec, dtype, device) -> Norm:
 
 def build_position(spec, dtype, device) -> PositionEncoding:
     return _build(_POSITIONS, "position encoding", spec, dtype, device)
+
+
+def build_embedding(spec, dtype, device) -> TokenEmbedding:
+    return _build(_EMBEDDINGS, "embedding", spec, dtype, device)
+
+
+def build_lm_head(spec, dtype, device) -> LogitsHead:
+    return _build(_LM_HEADS, "LM head", spec, dtype, device)
 
 
 def build_block(spec, dtype, device):

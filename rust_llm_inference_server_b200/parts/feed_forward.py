@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..ops.profile import span
 from .base import FeedForward, register_feed_forward
 
 
@@ -42,17 +43,19 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, step, sink=None):
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
-        if fusable and x.shape[0] <= ops.DECODE_GEMM_ROWS:
-            act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
-        elif fusable and x.shape[0] >= 128 and self.spec.intermediate % 128 == 0:
-            # prefill: the tcgen05 product with the gating in its epilogue (the gate|up activations
-            # never reach HBM)
-            act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu4")
-        else:
-            gu = ops.linear(x, self.w_gate_up)
-            act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
-            ops.swiglu(gu, act, self.interleave)
-        return ops.linear(act, self.w_down, sink=sink)
+        with span("mlp gate+up, silu*up"):
+            if fusable and x.shape[0] <= ops.DECODE_GEMM_ROWS:
+                act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
+            elif fusable and x.shape[0] >= 128 and self.spec.intermediate % 128 == 0:
+                # prefill: the tcgen05 product with the gating in its epilogue (the gate|up activations
+                # never reach HBM)
+                act = ops.gemm_tcgen05(x, self.w_gate_up, "swiglu4")
+            else:
+                gu = ops.linear(x, self.w_gate_up)
+                act = step.buffer("ffn_act", (x.shape[0], self.spec.intermediate), self.dtype)
+                ops.swiglu(gu, act, self.interleave)
+        with span("mlp down proj"):
+            return ops.linear(act, self.w_down, sink=sink)
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -6,6 +6,7 @@ import numpy as np
 import torch
 
 from .. import ops
+from ..ops.profile import span
 from .base import Norm, register_norm
 
 
@@ -30,11 +31,13 @@ class RMSNorm(Norm):
 
     def forward(self, resid, delta, step):
         out = step.buffer("norm_out", (resid.shape[0], self.dim), self.dtype)
-        return ops.rmsnorm(resid, self.weight, self.eps, out, delta)
+        with span("residual add + rms norm"):
+            return ops.rmsnorm(resid, self.weight, self.eps, out, delta)
 
     def forward_rows(self, resid, delta, step, rows):
         out = step.buffer("norm_rows_out", (rows.shape[0], self.dim), self.dtype)
-        return ops.rmsnorm(resid, self.weight, self.eps, out, delta, rows)
+        with span("residual add + rms norm"):
+            return ops.rmsnorm(resid, self.weight, self.eps, out, delta, rows)
 
     def sink(self, resid, step):
         if not ops.fuses_norms(resid.shape[0], self.dtype, self.dim):

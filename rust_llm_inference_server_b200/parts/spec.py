@@ -66,6 +66,30 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """Token table: row `id` of `weight` (vocab, dim) starts the residual stream, multiplied by
+    `scale` if one is given (the reference's Llama has none, crates/model/src/llama.rs:256-262)."""
+    vocab_size: int
+    dim: int
+    weight: str
+    scale: Optional[float] = None
+    kind: str = "embedding"
+
+
+@dataclass(frozen=True)
+class LMHeadSpec:
+    """Logits = h · weight^T in float32 (crates/model/src/llama.rs:279-285), then, where given,
+    multiplied by `logit_scale` and capped smoothly: cap · tanh(logits / cap).  `weight` may name
+    the embedding's tensor (tied)."""
+    vocab_size: int
+    dim: int
+    weight: str
+    logit_scale: Optional[float] = None
+    soft_cap: Optional[float] = None
+    kind: str = "lm_head"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block.  arrangement "prenorm": x += mixer(norm1(x)); x += feed_forward(norm2(x))
     (crates/model/src/llama.rs:264-271)."""
@@ -91,11 +115,11 @@ class LayerCall:
 class ModelSpec:
     vocab_size: int
     hidden: int
-    embedding: str                   # (vocab, hidden)
+    embedding: Any                   # an EmbeddingSpec, or just the tensor's name (vocab, hidden)
     layers: tuple
     order: tuple                     # of LayerCall
     final_norm: Any
-    lm_head: str                     # (vocab, hidden); equals `embedding` when tied
+    lm_head: Any                     # an LMHeadSpec, or just the tensor's name (the embedding's when tied)
     max_positions: int
     # names that a checkpoint may hold although the model does not read them
     ignorable: tuple = ()

@@ -48,8 +48,17 @@ class PlacedSource(TensorSource):
         self.ckpt = ckpt
         self.compute_dtype = compute_dtype
         self.device = device
+        self._shared: dict = {}
 
-    def get(self, name: str, role: str = "matrix") -> torch.Tensor:
+    def get(self, name: str, role: str = "matrix", share: bool = False) -> torch.Tensor:
+        if share:
+            key = (name, role)
+            if key not in self._shared:
+                self._shared[key] = self._place(name, role)
+            return self._shared[key]
+        return self._place(name, role)
+
+    def _place(self, name: str, role: str) -> torch.Tensor:
         t = self.ckpt.get(name)
         if role == "matrix":
             if not t.dtype.is_floating_point:

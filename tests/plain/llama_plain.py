@@ -160,16 +160,19 @@ def lm_head_weight(w: dict, cfg: dict):
     return w["lm_head.weight"]
 
 
-def forward_logits(w: dict, cfg: dict, tokens) -> torch.Tensor:
+def forward_logits(w: dict, cfg: dict, tokens, rows=None) -> torch.Tensor:
     """crates/model/src/llama.rs:218-311 for one whole sequence: float32 logits (len, vocab)
-    at every position."""
-    w = {k: v.to(torch.float32) for k, v in w.items()}
+    at every position, or at the positions `rows` only (llama.rs:296-305 selects rows before the
+    LM head in the same way)."""
+    w = {k: v if v.dtype == torch.float32 else v.to(torch.float32) for k, v in w.items()}
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     positions = torch.arange(len(ids))
     x = embedding(ids, w["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, i, cfg, positions)
     x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     return linear(x, lm_head_weight(w, cfg))
 
 

@@ -33,7 +33,7 @@ def test_every_size_comes_from_the_file():
     a, b = LlamaConfig.from_dict(TINY_A), LlamaConfig.from_dict(TINY_B)
     sa, sb = describe_llama(a), describe_llama(b)
     assert (len(sa.layers), len(sb.layers)) == (2, 3)
-    assert sa.lm_head == sa.embedding and sb.lm_head == "lm_head.weight"
+    assert sa.lm_head.weight == sa.embedding.weight and sb.lm_head.weight == "lm_head.weight"
     m = sb.layers[1].mixer
     assert (m.n_heads, m.n_kv_heads, m.head_dim, m.hidden) == (3, 1, 32, 96)
     assert m.position.scaling.factor == 32.0 and m.position.theta == 500000.0

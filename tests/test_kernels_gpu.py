@@ -404,7 +404,7 @@ def test_prefill_flash_attention_over_pages(geom, ps, window):
         # the tcgen05 kernel lets 1, 2 or 4 CTAs of a cluster share a tile's blocks of keys (some then
         # have no block at all); 0: its own choice from the number of tiles and the longest context
         for splits in (1, 2, 4, 0):
-            lib().rlis_attention_prefill_tc_set_splits(splits)
+            ops.debug_set("prefill_splits", splits)
             out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
             ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu),
                                   dev(torch.tensor(lens, dtype=torch.int32)), dev(tables), nh, nkv, d, ps,
@@ -412,7 +412,7 @@ def test_prefill_flash_attention_over_pages(geom, ps, window):
             err = (out.float().cpu().view(-1, nh, d) - want).abs().max()
             assert err <= 2.5e-2, (splits, err)
     finally:
-        lib().rlis_attention_prefill_tc_set_splits(0)
+        ops.debug_set("prefill_splits", 0)
     ops.check_device_errors()
 
 
@@ -432,6 +432,44 @@ def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
         got = out.float().cpu().view(m, 8, 64)
         assert (got - want).abs().max() <= 3e-2
         assert ((got[qi] - 7.0).abs().max() < 0.05) == seen, (qi, key)
+
+
+@pytest.mark.parametrize("geom,tcgen05", [((8, 2, 64), True), ((8, 2, 64), False), ((6, 3, 128), False), ((4, 4, 64), False)])
+@pytest.mark.parametrize("W", [70, 129])
+def test_prefill_flash_attention_window_edge(geom, tcgen05, W):
+    """With a window of W keys, the query at position p sees the key at p - W + 1 and not the one at
+    p - W.  The softmax of one query row sits on exactly that key: rows at the start and at the end
+    of a tile (the first visible key differs from row to row inside a tile), a portion deep in its
+    context, pages behind every row's window gone from the block table, the tcgen05 and the
+    mma.sync kernel, and 1, 2 and 4 CTAs sharing a tile's keys."""
+    from rust_llm_inference_server_b200 import ops
+    nh, nkv, d = geom
+    ps, n, m = 16, 1000, 200
+    cu = torch.tensor([0, m], dtype=torch.int32)
+    tiles = torch.tensor([(0, t0) for t0 in range(0, m, 64)], dtype=torch.int32)
+    first = n - m
+    ops.debug_set("prefill_tcgen05", 1 if tcgen05 else 0)
+    try:
+        for qi in (0, 1, 63, 64, 127, 128, 199):
+            p = first + qi
+            for key, seen in ((p - W + 1, True), (p - W, False), (p, True)):
+                q, kc, vc, tables, sot, pos, want = attention_case(geom, [n], [m], ps, torch.bfloat16, window=W,
+                                                                   seed=qi + key, spike=(0, qi, key))
+                tables = tables.clone()
+                tables[0, :(first - W + 1) // ps] = -1          # no row of the portion looks that far back
+                for splits in ((0, 1, 2, 4) if tcgen05 else (0,)):
+                    ops.debug_set("prefill_splits", splits)
+                    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+                    ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu),
+                                          dev(torch.tensor([n], dtype=torch.int32)), dev(tables), nh, nkv, d, ps,
+                                          1 / math.sqrt(d), W, n)
+                    got = out.float().cpu().view(m, nh, d)
+                    assert (got - want).abs().max() <= 3e-2, (qi, key, splits)
+                    assert ((got[qi] - 7.0).abs().max() < 0.05) == seen, (qi, key, splits)
+    finally:
+        ops.debug_set("prefill_splits", 0)
+        ops.debug_set("prefill_tcgen05", 1)
+    ops.check_device_errors()
 
 
 def test_decode_attention_far_key_and_window():
@@ -533,11 +571,11 @@ def test_filtered_sampling_cluster_and_one_cta_kernels_agree(V):
     lt = torch.from_numpy(logits).cuda()[:, :V]                       # rows with a stride, not 16-byte aligned
     pt = torch.from_numpy(params.view(np.int32)).cuda()
     got = ops.sample_filtered(lt, pt).cpu().tolist()
-    lib().rlis_sample_filtered_set_cluster(0)
+    ops.debug_set("filtered_cluster", 0)
     try:
         want = ops.sample_filtered(lt, pt).cpu().tolist()
     finally:
-        lib().rlis_sample_filtered_set_cluster(1)
+        ops.debug_set("filtered_cluster", 1)
     assert got == want
     assert got[3] < V and all(0 <= t < V for t in got)
 

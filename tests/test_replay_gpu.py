@@ -27,7 +27,8 @@ TOL_BETWEEN_MODES = {"float32": 1e-5, "bfloat16": 2e-2}
 def requests_for(which: str, seed: int = 1) -> dict:
     cfg = CONFIGS[which]
     rng = np.random.default_rng(seed)
-    lens = {"A": [1, 7, 13, 32, 100], "B": [3, 50, 97, 200, 64, 17], "C": [130, 33, 2, 71, 40]}[which]
+    lens = {"A": [1, 7, 13, 32, 100], "B": [3, 50, 97, 200, 64, 17], "C": [130, 33, 2, 71, 40],
+            "D": [300, 150, 40, 2, 200, 129], "E": [260, 31, 140, 5, 90]}[which]
     return {f"r{i}": rng.integers(0, cfg["vocab_size"], size=n).tolist() for i, n in enumerate(lens)}
 
 
@@ -42,9 +43,22 @@ def plain_logits(model_root, which):
     return _plain_cache[which]
 
 
-def session(model_root, which, dtype, max_tokens):
+def session(model_root, which, dtype, max_tokens, page_size=16):
     from rust_llm_inference_server_b200.engine.replay import ReplaySession
-    return ReplaySession(make_model_dir(model_root, which), dtype, max_tokens)
+    return ReplaySession(make_model_dir(model_root, which), dtype, max_tokens, page_size)
+
+
+# Which kernels a configuration's bfloat16 replay has to go through (names of
+# `ops.launches_by_kernel`): a configuration that silently took a slower path would still give the
+# right logits.
+KERNELS_BF16 = {
+    "D": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma",
+          "gemm_tcgen05.swiglu4", "stream_gemm.sink", "stream_gemm.scaled", "stream_gemm.scaled.swiglu",
+          "rope_cache", "rmsnorm", "rmsnorm.rows", "embedding"],
+    "E": ["attention_prefill.mma", "attention_decode.mma", "attention_decode_qkv.mma", "stream_gemm.sink",
+          "stream_gemm.scaled"],
+    "A": ["attention_generic", "attention_decode.cuda_core"],
+}
 
 
 def compare(got: dict, ref: dict, tol: float, what: str):
@@ -59,8 +73,10 @@ def compare(got: dict, ref: dict, tol: float, what: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C"])
-def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, dtype):
+@pytest.mark.parametrize("which,page", [("A", 16), ("A", 8), ("B", 16), ("C", 16), ("D", 16), ("D", 32), ("E", 16), ("E", 64)])
+def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, dtype):
+    from rust_llm_inference_server_b200 import ops
+    ops.launches_by_kernel.clear()
     reqs = requests_for(which)
     ref = plain_logits(model_root, which)
     families = {
@@ -72,8 +88,10 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, dtype):
     }
     results = {}
     for fam, steps in families.items():
-        s = session(model_root, which, dtype, R.live_token_peak(steps))   # the smallest pool allowed
+        s = session(model_root, which, dtype, R.live_token_peak(steps), page)   # the smallest pool allowed
         results[fam] = R.collect(s.step, steps)
+        if dtype == "bfloat16" and fam == "decode" and which in ("D", "E"):
+            assert s.runner._graph_launches > 0            # single tokens ran from captured graphs
         assert s.cache.check_invariants() == ""
         assert s.cache.num_free_pages(0) == s.cache.group(0).num_pages, fam   # everything given back
         compare(results[fam], ref, TOL[dtype], f"{which} {dtype} {fam} vs plain")
@@ -82,6 +100,13 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, dtype):
         sub = {k: v for k, v in results[fam].items()}
         worst = max(float(np.abs(v - whole[k]).max()) for k, v in sub.items())
         assert worst <= TOL_BETWEEN_MODES[dtype], f"{which} {dtype}: {fam} differs from whole by {worst}"
+    if dtype == "bfloat16":
+        missing = [k for k in KERNELS_BF16.get(which, []) if not ops.launches_by_kernel.get(k)]
+        assert not missing, f"{which}: never launched {missing}; launched {sorted(ops.launches_by_kernel)}"
+    else:
+        fast = [k for k in ops.launches_by_kernel if "tcgen05" in k or "mma" in k or "stream_gemm" in k]
+        assert not fast, f"the float32 path went through {fast}"
+    ops.check_device_errors()
 
 @pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_norms_inside_the_products_and_norms_as_kernels_agree(model_root, which, monkeypatch):
@@ -133,7 +158,8 @@ def test_trace_run_program(model_root, tmp_path):
         out_dir = tmp_path / dtype
         proc = subprocess.run(
             [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", make_model_dir(model_root, which),
-             "--dtype", dtype, "--out", str(out_dir), "--max-tokens", str(R.live_token_peak(steps))],
+             "--dtype", dtype, "--out", str(out_dir), "--max-tokens", str(R.live_token_peak(steps))]
+            + (["--page-size", "8"] if dtype == "float32" else []),
             input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
         assert proc.returncode == 0, proc.stderr[-2000:]
         assert proc.stdout.split("\n")[:len(steps)] == [f"done {s['step']}" for s in steps]

@@ -236,3 +236,138 @@ def test_a_step_ahead_with_placeholders_registers_the_real_tokens():
     assert [tuple(x) for x in seqs] == [(1, 8, 9)] and s.cached_tokens() == 8
     # had the page been registered with the placeholder, this request would have found one page only
     assert s.check() == ""
+
+
+class FakeAheadEngine:
+    """The engine's loop with decode-ahead (engine/engine.py: step, _may_run_ahead, _launch,
+    _collect) over the host module alone: tokens are "sampled" as a function of the request and
+    the position, so that the outcome can be compared with a loop that never runs ahead."""
+
+    def __init__(self, s, prompts, max_tokens, check_pages=True, ahead=True):
+        self.s, self.cache = s, s.cache()
+        self.tokens = {i: list(p) for i, p in enumerate(prompts)}
+        self.prompt_len = {i: len(p) for i, p in enumerate(prompts)}
+        self.max_tokens, self.check_pages, self.ahead = max_tokens, check_pages, ahead
+        self.done, self.inflight, self.fallbacks, self.preemptions, self.ahead_steps = {}, None, 0, 0, 0
+        for i, p in enumerate(prompts):
+            s.add(i, p)
+
+    @staticmethod
+    def sample(sid, pos):
+        return (sid * 31 + pos * 7) % 97 + 1
+
+    def may_run_ahead(self, cur):
+        seqs, rows = cur
+        if not self.ahead or not rows or len(rows) != len(seqs) or self.s.num_waiting():
+            return False
+        if any(sid not in self.tokens or len(self.tokens[sid]) + 1 - self.prompt_len[sid] >= self.max_tokens
+               for sid in rows):
+            return False
+        if self.check_pages:
+            need = sum(self.cache.pages_needed(sid, 0, len(self.tokens[sid]) + 1) for sid in rows)
+            if need > self.cache.num_free_pages(0):
+                return False
+        return True
+
+    def launch(self, prev):
+        if prev is not None:
+            for sid in prev[1]:
+                self.s.append_token(sid, 0)
+        seqs, pre = self.s.schedule()
+        seqs = [tuple(x) for x in seqs]
+        self.preemptions += len(pre)
+        if prev is not None:
+            want = [(sid, len(self.tokens[sid]), len(self.tokens[sid]) + 1) for sid in prev[1]]
+            if pre or seqs != want:
+                for sid in prev[1]:
+                    self.s.drop_last_token(sid)
+                self.fallbacks += 1
+                return None
+            self.ahead_steps += 1
+            return (seqs, list(prev[1]))
+        if not seqs:
+            assert not self.s.has_work(), "no progress with work pending"
+            return None
+        rows = [sid for sid, b, e in seqs if e == len(self.tokens[sid])]
+        for sid, b, e in seqs:
+            self.s.advance(sid, e)
+        return (seqs, rows)
+
+    def collect(self, cur, nxt):
+        for sid in cur[1]:
+            if sid not in self.tokens:
+                continue
+            t = self.tokens[sid]
+            t.append(self.sample(sid, len(t)))
+            if len(t) - self.prompt_len[sid] >= self.max_tokens:
+                self.done[sid] = self.tokens.pop(sid)
+                self.s.remove(sid)
+            elif nxt is not None:
+                self.s.set_token(sid, len(t) - 1, t[-1])
+            else:
+                self.s.append_token(sid, t[-1])
+        if nxt is not None:
+            for sid, b, e in nxt[0]:
+                if sid in self.tokens:
+                    self.s.advance(sid, e)
+
+    def run(self):
+        for _ in range(100000):
+            if not self.s.has_work() and self.inflight is None:
+                return self.done
+            cur, self.inflight = self.inflight, None
+            if cur is None:
+                cur = self.launch(None)
+                if cur is None:
+                    continue
+            nxt = self.launch(cur) if self.may_run_ahead(cur) else None
+            self.collect(cur, nxt)
+            self.inflight = nxt
+            assert self.s.check() == ""
+            for sid, t in self.tokens.items():           # the scheduler's copy agrees with the engine's
+                n = self.s.num_tokens(sid)
+                assert self.s.tokens(sid, 0, len(t)) == t and n in (len(t), len(t) + 1)
+        raise AssertionError("did not finish")
+
+
+@pytest.mark.parametrize("case", [
+    dict(pages=5, page=8, prompts=[8, 8], max_tokens=24),        # two requests, nobody waiting when pages run out
+    dict(pages=4, page=16, prompts=[16, 16], max_tokens=40),
+    dict(pages=9, page=4, prompts=[5, 9, 3], max_tokens=17),
+])
+def test_decode_ahead_never_meets_a_preemption_and_falls_back_when_it_would(case):
+    """With too few pages for every running request to grow, a decode step has to preempt
+    (crates/engine/src/scheduler.rs:227-246).  The engine asks the cache before it launches a step
+    ahead, so the step that preempts is an ordinary one; without that check the plan of the step
+    ahead differs from what was expected, the placeholders are taken back, and the loop goes on
+    step by step.  Either way: the tokens of a loop that never runs ahead, all pages back."""
+    def run(**kw):
+        s = sched(case["pages"], block_size=case["page"], max_seqs=4, prefix=True)
+        e = FakeAheadEngine(s, [toks(i + 1, n) for i, n in enumerate(case["prompts"])], case["max_tokens"], **kw)
+        done = e.run()
+        assert s.cache().num_free_pages(0) == case["pages"] and s.check() == ""
+        return done, e
+    base, eb = run(ahead=False)
+    assert eb.preemptions > 0 and len(base) == len(case["prompts"])
+    checked, ec = run()
+    assert checked == base and ec.preemptions > 0 and ec.fallbacks == 0 and ec.ahead_steps > 0
+    unchecked, eu = run(check_pages=False)
+    assert unchecked == base and eu.preemptions > 0 and eu.fallbacks > 0
+
+
+def test_a_token_sampled_for_a_request_that_was_preempted_meanwhile_is_kept():
+    s = sched(3, block_size=4, max_seqs=2, watermark=0)
+    s.add(0, toks(1, 4)); s.add(1, toks(2, 4))
+    seqs, _ = s.schedule()
+    for sid, b, e in seqs:
+        s.advance(sid, e)
+    s.append_token(0, 7); s.append_token(1, 7)            # both need a second page; one is left
+    seqs, pre = s.schedule()
+    assert [tuple(x) for x in seqs] == [(0, 4, 5)] and pre == [1]
+    s.append_token(1, 9)                                  # the token of a step launched before the preemption
+    assert s.tokens(1, 0, 6) == toks(2, 4) + [7, 9]
+    s.drop_last_token(1)
+    assert s.num_tokens(1) == 5
+    s.drop_last_token(0)                                  # request 0: five tokens, four of them computed
+    with pytest.raises(RuntimeError):
+        s.drop_last_token(0)                              # a computed token is never taken back

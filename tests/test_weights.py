@@ -58,7 +58,7 @@ def test_tied_model_ignores_a_stored_lm_head_and_untied_needs_it():
     t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)
     m = build_model(TINY_A, "bfloat16", "cpu")
     m.load(Checkpoint(tensors=t))
-    assert m.lm_head is m.embed
+    assert m.lm_head.weight is m.embedding.weight
     tb = random_tensors(TINY_B, 2)
     del tb["lm_head.weight"]
     with pytest.raises(WeightError):
@@ -81,7 +81,7 @@ def test_element_type_policy():
     t32 = random_tensors(TINY_A, 0, "float32")
     m = build_model(TINY_A, "float32", "cpu")
     m.load(Checkpoint(tensors=t32))
-    assert torch.equal(m.embed, t32["model.embed_tokens.weight"])
+    assert torch.equal(m.embedding.weight, t32["model.embed_tokens.weight"])
 
 
 def test_random_model_folder_is_seeded_and_order_independent(tmp_path):

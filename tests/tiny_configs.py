@@ -35,8 +35,44 @@ TINY_C = {
     "max_position_embeddings": 512, "tie_word_embeddings": True,
 }
 
-SEEDS = {"A": 0, "B": 2, "C": 7}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Head size 64 with query heads in pairs, widths that are multiples of 128: in bfloat16 this one runs
+# the kernels that the large models run (tcgen05 prefill attention, tensor-core decode attention with
+# keys by bulk tensor copies and its own rotation, the tcgen05 gate|up product with the gating in its
+# epilogue, the streaming products with the norms in their epilogues, decode steps from graphs).
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 2,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 1000,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "max_position_embeddings": 1024, "tie_word_embeddings": True,
+}
+
+# Head size 128 in groups of three (the mma.sync flash kernel and the 128-wide decode kernel).
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 320, "intermediate_size": 448, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 777,
+    "rms_norm_eps": 2e-6, "rope_theta": 100000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 96},
+    "max_position_embeddings": 1024, "tie_word_embeddings": False,
+}
+
+# The layer sizes of Llama 3.2 1B with two layers (the sizes the benchmark runs at).
+ONE_B_2L = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 2,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072, "tie_word_embeddings": True,
+}
+
+SEEDS = {"A": 0, "B": 2, "C": 7, "D": 11, "E": 13, "1B2L": 4}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "1B2L": ONE_B_2L}
 
 
 def make_model_dir(tmp_root: str, which: str, store_dtype: str = "bfloat16") -> str:
