@@ -39,6 +39,26 @@ CONFIG_1B = {
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 SEED = 4
+
+# configs[3] and configs[4] of the baseline description: Llama-3.2-3B and Llama-3.1-8B sizes
+CONFIG_3B = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 3072, "intermediate_size": 8192, "num_hidden_layers": 28,
+    "num_attention_heads": 24, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True,
+}
+CONFIG_8B = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False,
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -110,10 +130,12 @@ class ClockSampler:
 
 
 def weight_bytes(cfg: dict, n_layers: int, elem: int = 2) -> int:
+    """What a decode step reads of the weights: every layer's matrices and the LM head's table once
+    (the embedding rows of a few tokens do not count)."""
     H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nh, nkv, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
     per_layer = ((nh + 2 * nkv) * d * H + H * nh * d + 3 * I * H) * elem + 2 * H * 4
-    return n_layers * per_layer + V * H * elem + H * 4      # LM head (tied table) read once
+    return n_layers * per_layer + V * H * elem + H * 4
 
 
 def kv_bytes_per_token(cfg: dict, n_layers: int, elem: int = 2) -> int:
@@ -186,6 +208,217 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: 
     return ms, launches / steps
 
 
+def percentile(xs, q):
+    if not xs:
+        return None
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(q / 100.0 * (len(xs) - 1))))]
+
+
+def serve_poisson(llm, prompts, outputs, arrivals, torch):
+    """Feeds requests to the engine loop as their arrival times come (wall clock) and steps it
+    until all have finished.  Returns per-request time to first token (from the intended arrival),
+    the gaps between a request's tokens, and the wall time from the first arrival to the last token."""
+    from rust_llm_inference_server_b200 import SamplingParams
+    eng = llm.engine
+    n = len(prompts)
+    first, last, gaps, done = {}, {}, [], {}
+    nxt = 0
+    rid_of = {}
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while len(done) < n:
+        now = time.perf_counter() - t0
+        while nxt < n and arrivals[nxt] <= now:
+            rid = eng.add_request(prompts[nxt], SamplingParams(max_tokens=outputs[nxt], ignore_eos=True))
+            rid_of[rid] = nxt
+            nxt += 1
+        if not eng.has_work():
+            time.sleep(max(0.0, min(0.001, arrivals[nxt] - now)))
+            continue
+        finished = eng.step()
+        t = time.perf_counter() - t0
+        for rid in eng.last_step.new_tokens:
+            i = rid_of[rid]
+            if i not in first:
+                first[i] = t - arrivals[i]
+            else:
+                gaps.append(t - last[i])
+            last[i] = t
+        for o in finished:
+            done[rid_of[o.request_id]] = o
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    return first, gaps, wall, done
+
+
+def workload_3b(args, torch, np) -> dict:
+    """configs[3]: 64 requests, prompts U[128, 2048], outputs U[64, 512], seeded Poisson arrivals,
+    prompts cut into portions of 512 tokens, through `LLMEngine.add_request` / `step` (the numbers
+    the reference publishes for its server sweep, README.md:187-191,208-214: throughput, time to the
+    first token, time between tokens, preemptions, prefix hits)."""
+    from rust_llm_inference_server_b200 import LLM
+    cfg = dict(CONFIG_3B)
+    n_full = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or n_full
+    rng = np.random.default_rng(5)
+    n = 64
+    p_lens = rng.integers(128, 2049, size=n).tolist()
+    o_lens = rng.integers(64, 513, size=n).tolist()
+    prompts = [rng.integers(0, cfg["vocab_size"], size=k).tolist() for k in p_lens]
+    arrivals = np.cumsum(rng.exponential(1.0 / args.rate, size=n)).tolist()
+    page = 16
+    kv_tok = kv_bytes_per_token(cfg, cfg["num_hidden_layers"])
+    runs = {}
+    llm = None
+    for name, pool_tokens in (("roomy", sum(p + o for p, o in zip(p_lens, o_lens)) + 64 * page),
+                              ("tight", 40960)):
+        del llm
+        torch.cuda.empty_cache()
+        llm = LLM.from_random(cfg, 5, dtype="bfloat16", on_device=True, max_seq_len=2048 + 512 + page,
+                              num_blocks=pool_tokens // page, block_size=page, max_num_seqs=64,
+                              max_batched_tokens=512, prefix_caching=True)
+        # warm-up: every kernel and graph shape once, outside the timed region
+        w_prompts = [rng.integers(0, cfg["vocab_size"], size=k).tolist() for k in (700, 130, 1500, 260)]
+        serve_poisson(llm, w_prompts, [24, 40, 16, 33], [0.0, 0.0, 0.01, 0.02], torch)
+        st = llm.engine.stats
+        pre0, hit0, steps0 = st.preemptions, st.prefix_hit_tokens, st.steps
+        clocks = ClockSampler()
+        clocks.start()
+        time.sleep(0.3)
+        first, gaps, wall, done = serve_poisson(llm, prompts, o_lens, arrivals, torch)
+        clk = clocks.stop()
+        assert all(len(done[i].token_ids) == o_lens[i] for i in range(n))
+        out_tokens = sum(o_lens)
+        ms = lambda x: None if x is None else round(x * 1e3, 2)
+        runs[name] = {
+            "pool_tokens": pool_tokens, "pool_gb": round(pool_tokens * kv_tok / 2 ** 30, 2),
+            "wall_s": round(wall, 3), "output_tokens_per_s": round(out_tokens / wall, 1),
+            "total_tokens_per_s": round((out_tokens + sum(p_lens)) / wall, 1),
+            "ttft_ms_p50": ms(percentile(list(first.values()), 50)), "ttft_ms_p99": ms(percentile(list(first.values()), 99)),
+            "itl_ms_p50": ms(percentile(gaps, 50)), "itl_ms_p99": ms(percentile(gaps, 99)),
+            "preemptions": st.preemptions - pre0, "prefix_hit_tokens": st.prefix_hit_tokens - hit0,
+            "steps": st.steps - steps0, "failed": st.failed_requests, "clocks": clk,
+        }
+    return {
+        "workload": "3b", "metric": "continuous batching, 64 requests in a Poisson stream (Llama-3.2-3B sizes, random bf16 weights)",
+        "impl": "ours", "dtype": "bf16", "n_gpus": 1,
+        "data": "synthetic: uniform-random token ids, random-init weights N(0,0.02) seed 5 (device generator)",
+        "config": {"model": "llama-3.2-3b-sizes", "layers": cfg["num_hidden_layers"], "layers_in_config": n_full,
+                   "hidden": 3072, "heads": 24, "kv_heads": 8, "head_dim": 128, "intermediate": 8192, "vocab": 128256,
+                   "requests": n, "prompt_tokens": sum(p_lens), "output_tokens": sum(o_lens), "rate_per_s": args.rate,
+                   "max_batched_tokens": 512, "max_num_seqs": 64, "page_size": page, "prefix_caching": True},
+        "runs": runs,
+    }
+
+
+def workload_8b(args, torch, np) -> dict:
+    """configs[4]: 32 requests with 2,048-token prompts, a quarter of which share their first
+    1,024 tokens, through the engine (prefill in portions, prefix reuse), then device-timed decode
+    steps of the 32 whose context ends at 8,192 tokens, against the HBM roofline."""
+    from rust_llm_inference_server_b200 import LLM, SamplingParams
+    cfg = dict(CONFIG_8B)
+    n_full = cfg["num_hidden_layers"]
+    n_layers = args.layers or n_full
+    cfg["num_hidden_layers"] = n_layers
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(6)
+    B, ctx, page = 32, 8192, 16
+    llm = LLM.from_random(cfg, 6, dtype="bfloat16", on_device=True, max_seq_len=ctx + page,
+                          num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                          max_batched_tokens=2048, prefix_caching=True)
+    V = cfg["vocab_size"]
+    shared = rng.integers(0, V, size=1024).tolist()
+    prompts = [(shared + rng.integers(0, V, size=1024).tolist()) if i % 4 == 0 else rng.integers(0, V, size=2048).tolist()
+               for i in range(B)]
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    llm.generate([rng.integers(0, V, size=300).tolist()], SamplingParams(max_tokens=4, ignore_eos=True))   # warm-up
+    st = llm.engine.stats
+    hit0 = st.prefix_hit_tokens
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, sp)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    assert all(len(o.token_ids) == 16 for o in outs)
+    engine_part = {"prompt_tokens": 2048 * B, "prefix_hit_tokens": st.prefix_hit_tokens - hit0, "wall_s": round(wall, 3),
+                   "prompt_tokens_per_s": round(2048 * B / wall, 1), "preemptions": st.preemptions}
+    steps = min(args.steps, 64)
+    clocks = ClockSampler()
+    ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch, clocks=clocks)
+    clk = clocks.stop()
+    mean_ctx = ctx - steps / 2
+    step_bytes = weight_bytes(cfg, n_layers) + B * mean_ctx * kv_bytes_per_token(cfg, n_layers)
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    return {
+        "workload": "8b", "metric": "decode tokens/s, batch 32, context 8192 (Llama-3.1-8B sizes, random bf16 weights)",
+        "value": round(B / (ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 4), "steps": steps, "warmup": args.warmup,
+        "impl": "ours", "dtype": "bf16", "n_gpus": 1,
+        "data": "synthetic: uniform-random token ids, random-init weights N(0,0.02) seed 6 (device generator)",
+        "config": {"model": "llama-3.1-8b-sizes", "layers": n_layers, "layers_in_config": n_full, "hidden": 4096,
+                   "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336, "vocab": V, "tied": False,
+                   "global_batch": B, "seq_len": ctx, "page_size": page, "kv_dtype": "bf16"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src,
+                     "bytes_per_step": int(step_bytes)},
+        "prompts_through_the_engine": engine_part, "gpu_launches": int(round(launches * steps)), "clocks": clk,
+    }
+
+
+def workload_1b_fp32(args, torch, np) -> dict:
+    """The true 32-bit path at the 1B sizes: a 2,048-token prefill and decode steps of a batch of 8
+    at a context of 4,096 (FFMA products, float32 cache and attention; no tensor cores)."""
+    from rust_llm_inference_server_b200 import LLM
+    from rust_llm_inference_server_b200.engine import StepEntry
+    cfg = dict(CONFIG_1B)
+    n_full = cfg["num_hidden_layers"]
+    n_layers = args.layers or n_full
+    cfg["num_hidden_layers"] = n_layers
+    B, ctx, page = 8, CONTEXT, 16
+    llm = LLM.from_random(cfg, SEED, dtype="float32", on_device=True, max_seq_len=ctx + page,
+                          num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                          max_batched_tokens=2048, prefix_caching=False)
+    runner, cache = llm.engine.runner, llm.engine.cache
+    rng = np.random.default_rng(0)
+    pre = []
+    for it in range(4):
+        sid = 500 + it
+        cache.acquire_state_slot(sid)
+        assert cache.reserve(sid, PREFILL_TOKENS)
+        toks = rng.integers(0, cfg["vocab_size"], size=PREFILL_TOKENS).tolist()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        runner.step([StepEntry(sid, toks, 0, [PREFILL_TOKENS - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        pre.append(s.elapsed_time(e))
+        cache.free(sid)
+    prefill_ms = statistics.median(pre[1:])
+    steps = min(args.steps, 32)
+    clocks = ClockSampler()
+    ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch, clocks=clocks)
+    clk = clocks.stop()
+    pk, pk_src = peaks()
+    step_bytes = weight_bytes(cfg, n_layers, 4) + B * (ctx - steps / 2) * kv_bytes_per_token(cfg, n_layers, 4)
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    return {
+        "workload": "1b-fp32", "metric": "decode tokens/s, batch 8, context 4096, true float32 path (Llama-3.2-1B sizes)",
+        "value": round(B / (ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 4), "steps": steps, "warmup": args.warmup,
+        "impl": "ours", "dtype": "fp32", "n_gpus": 1,
+        "config": {"model": "llama-3.2-1b-sizes", "layers": n_layers, "layers_in_config": n_full, "global_batch": B,
+                   "seq_len": ctx, "page_size": page, "kv_dtype": "fp32"},
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
+                    "tflops": round(prefill_flops(cfg, n_layers, PREFILL_TOKENS) / (prefill_ms / 1e3) / 1e12, 2)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src},
+        "gpu_launches": int(round(launches * steps)), "clocks": clk,
+    }
+
+
+WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -199,6 +432,15 @@ def main() -> int:
                     help="with --only decode: do not compute the cached context first (keeps profiler captures short)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run one part only and print a short line (for profiler captures of a small case)")
+    ap.add_argument("--sizes", default="1b", choices=["1b", "3b", "8b"],
+                    help="with --only: the layer sizes to run it at (the default line is always the 1B's)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="one of the other measured configurations instead of the default line: 3b (continuous "
+                         "batching under a Poisson stream), 8b (batch 32 at 8,192 of context), 1b-fp32")
+    ap.add_argument("--rate", type=float, default=48.0, help="--workload 3b: mean arrivals a second")
+    ap.add_argument("--spans", action="store_true",
+                    help="with --only: time the stages of the step with CUDA-event spans (RLIS_PROFILE) and "
+                         "print the table to stderr; steps then run eagerly, not from graphs")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -211,9 +453,13 @@ def main() -> int:
     import torch
 
     from rust_llm_inference_server_b200 import LLM, SamplingParams
+    from rust_llm_inference_server_b200.ops import profile
 
+    if args.workload:
+        print(json.dumps(WORKLOADS[args.workload](args, torch, np)))
+        return 0
     pk, pk_src = peaks()
-    cfg = dict(CONFIG_1B)
+    cfg = dict({"1b": CONFIG_1B, "3b": CONFIG_3B, "8b": CONFIG_8B}[args.sizes if args.only else "1b"])
     n_layers_full = cfg["num_hidden_layers"]
     n_layers = args.layers or n_layers_full
     cfg["num_hidden_layers"] = n_layers
@@ -235,10 +481,14 @@ def main() -> int:
     rng = np.random.default_rng(0)
     V = cfg["vocab_size"]
     cache = llm.engine.cache
+    if args.only and args.spans:
+        profile.enable(True)
     if args.only == "decode":
         ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch, fill=not args.no_fill)
         print(json.dumps({"only": "decode", "batch": B, "context": context, "ms_per_step": round(ms, 4),
                           "launches_per_step": launches}))
+        if args.spans:
+            print(profile.format_report(profile.take_report()), file=sys.stderr)
         return 0
     pre_ms = []
     for it in range(5 if not args.only else args.warmup + args.steps):
@@ -257,6 +507,8 @@ def main() -> int:
     prefill_ms = statistics.median(pre_ms[2:] if not args.only else pre_ms[args.warmup:])
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3)}))
+        if args.spans:
+            print(profile.format_report(profile.take_report()), file=sys.stderr)
         return 0
     pf = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,

@@ -237,8 +237,14 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     __shared__ int s_table[DEC_TABLE_SLOTS];
     __shared__ uint64_t s_full[DEC_WARPS][NSTAGE];     // TMA: a stage of a warp has arrived
     __shared__ int s_abort;
-    // TMA (head size 64): rows of 128 bytes, the 128-byte swizzle instead of padding
-    constexpr int STRIDE = TMA ? D : D + 8;  // elements per row
+    // TMA: a tile of 32 rows is D / 64 sub-tiles of [32 rows][64 elements]: rows of 128 bytes under the
+    // 128-byte swizzle instead of padded rows (head size 128: the two halves of a row lie 4 KB apart)
+    constexpr int STRIDE = TMA ? D : D + 8;  // elements per row (padded rows; for the tile's size)
+    constexpr int HALVES = D / 64;           // TMA: sub-tiles of a tile
+    // element offset, within a K or V tile, of the 16-byte chunk `chunk` of row r
+    auto tile_off = [](int r, int chunk) -> int {
+        return TMA ? (chunk >> 3) * (32 * 64) + r * 64 + (((chunk & 7) ^ (r & 7)) << 3) : r * STRIDE + (chunk << 3);
+    };
     constexpr int KS = D / 16;               // k-steps of Q K^T
     constexpr int ND = D / 8;                // n-tiles of P V
     constexpr int CPR = D / 8;               // 16-byte chunks per row
@@ -292,9 +298,10 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     }
     const int key_in0 = lane / CPR, c16 = lane % CPR;       // chunk i of a lane: key_in0 + i * (32 / CPR)
     const uint32_t sm_off0 = (uint32_t)(key_in0 * STRIDE + c16 * 8);
-    // TMA: a block of 32 keys is 32 / min(page, 32) boxes of the cache seen as [rows, 64]; a box
-    // wholly past the context or behind the window is asked for past the end of the tensor and
-    // arrives as zeros.  One lane announces the bytes, then a lane per box issues its copy.
+    // TMA: a block of 32 keys is 32 / min(page, 32) boxes (times D / 64 column halves) of the cache
+    // seen as [rows, D]; a box wholly past the context or behind the window is asked for past the end
+    // of the tensor and arrives as zeros.  One lane announces the bytes, then a lane per box issues
+    // its copy.
     const int box_rows = page_size < 32 ? page_size : 32;
     const int boxes = 32 / box_rows;
     auto issue = [&](int blk, int stage) {
@@ -306,9 +313,10 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             __syncwarp();
             if (lane == 0) tc::bar_expect_tx(&s_full[warp][stage], 2 * 32 * D * 2);
             __syncwarp();
-            if (lane < 2 * boxes) {
+            if (lane < 2 * boxes * HALVES) {
                 const int bx = lane % boxes;
-                const bool is_v = lane >= boxes;
+                const int half = (lane / boxes) % HALVES;
+                const bool is_v = lane >= boxes * HALVES;
                 const int key = (blk << 5) + bx * box_rows;
                 const bool wanted = key < ctx && key + box_rows > lo_all;
                 int rowc = cache_rows;
@@ -318,8 +326,8 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
                     const int page = table_in_smem ? s_table[pi - page0] : table[pi];
                     rowc = (page * nkv + kvh) * page_size + in_page;
                 }
-                tc::tma_load_2d((is_v ? vs_ : ks_) + (size_t)bx * box_rows * D, is_v ? &map_v : &map_k, 0, rowc,
-                                &s_full[warp][stage]);
+                tc::tma_load_2d((is_v ? vs_ : ks_) + half * (32 * 64) + bx * box_rows * 64, is_v ? &map_v : &map_k,
+                                half * 64, rowc, &s_full[warp][stage]);
             }
         } else {
 #pragma unroll
@@ -440,9 +448,12 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             // slots of the last page past the context hold whatever was there before; a zero of P
             // times a NaN would still be a NaN: those rows of V are cleared (a lane per row)
             if ((blk << 5) + lane >= ctx) {
-                uint4* vr = reinterpret_cast<uint4*>(const_cast<bf16*>(vs_) + lane * STRIDE);
 #pragma unroll
-                for (int i = 0; i < D / 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
+                for (int hf = 0; hf < HALVES; ++hf) {
+                    uint4* vr = reinterpret_cast<uint4*>(const_cast<bf16*>(vs_) + hf * (32 * 64) + lane * 64);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) vr[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             __syncwarp();
         }
@@ -454,10 +465,10 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
             const int slot = fz.slots[row];
             if (slot >= 0) {
             const size_t at = (((size_t)(slot / page_size) * nkv + kvh) * page_size + (size_t)(slot % page_size)) * D;
-            bf16* kt = const_cast<bf16*>(ks_) + r * STRIDE;
-            bf16* vt = const_cast<bf16*>(vs_) + r * STRIDE;
-            // where element j of row r sits: with the swizzle, its 16-byte chunk is XORed with r % 8
-            auto at_el = [&](int j) { return TMA ? ((((j >> 3) ^ (r & 7)) << 3) | (j & 7)) : j; };
+            bf16* kt = const_cast<bf16*>(ks_);
+            bf16* vt = const_cast<bf16*>(vs_);
+            // where element j of row r sits (with the swizzle, its 16-byte chunk is XORed with r % 8)
+            auto at_el = [&](int j) { return tile_off(r, j >> 3) | (j & 7); };
             for (int j = lane; j < D / 2; j += 32) {
                 const float a = __bfloat162float(krow[j]), b = __bfloat162float(krow[j + D / 2]);
                 const bf16 k1 = from_f<bf16>(rope_first(a, b, s_cos[j], s_sin[j]));
@@ -486,7 +497,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
                 uint32_t kb[4];
                 // (swizzle: the 16-byte chunk index is XORed with the row's index in its group of 8)
                 const int kchunk = ks2 * 4 + (lane >> 3);
-                ldmatrix_x4(kb, ks_ + (nt * 8 + (lane & 7)) * STRIDE + ((TMA ? kchunk ^ (lane & 7) : kchunk) << 3));
+                ldmatrix_x4(kb, ks_ + tile_off(nt * 8 + (lane & 7), kchunk));
                 mma_bf16_16816(sacc[nt], qa[2 * ks2], kb[0], kb[1]);
                 mma_bf16_16816(sacc[nt], qa[2 * ks2 + 1], kb[2], kb[3]);
             }
@@ -537,7 +548,7 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
                 uint32_t vb[4];
                 const int mat = lane >> 3;
                 const int vchunk = nd2 * 2 + (mat >> 1);
-                ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * STRIDE + ((TMA ? vchunk ^ (lane & 7) : vchunk) << 3));
+                ldmatrix_x4_trans(vb, vs_ + tile_off(kk * 16 + (mat & 1) * 8 + (lane & 7), vchunk));
                 mma_bf16_16816(oacc[2 * nd2], pa, vb[0], vb[1]);
                 mma_bf16_16816(oacc[2 * nd2 + 1], pa, vb[2], vb[3]);
             }
@@ -783,18 +794,18 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
         // fewer rounds (four stages, one CTA an SM, measured slower at every size)
         if (stages == 0) stages = (ctas + 2 * sms - 1) / (2 * sms) <= (ctas + 3 * sms - 1) / (3 * sms) ? 3 : 2;
         if (d == 128 && stages > 3) stages = 3;               // 4 stages of 128-wide rows do not fit
-        // Head size 64 with pages of 8 tokens or more (that divide, or are divided by, a block of 32
-        // keys): the keys come by bulk tensor copies into swizzled tiles.  Needs the number of pages
-        // (the tensor's bounds); without it, and for the other sizes, 16-byte asynchronous copies.
+        // Pages of 8 tokens or more (that divide, or are divided by, a block of 32 keys): the keys come
+        // by bulk tensor copies into swizzled tiles.  Needs the number of pages (the tensor's bounds);
+        // without it, and for other page sizes, 16-byte asynchronous copies.
         const long long cache_rows = (long long)n_pages * nkv * page_size;
-        bool tma = g_decode_tma && d == 64 && n_pages > 0 && page_size >= 8 &&
+        bool tma = g_decode_tma && n_pages > 0 && page_size >= 8 &&
                    (32 % page_size == 0 || page_size % 32 == 0) && cache_rows < (1ll << 31) &&
                    ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
         CUtensorMap map_k = {}, map_v = {};
         if (tma) {
             const int box_rows = page_size < 32 ? page_size : 32;
-            tma = tc::make_map(&map_k, k_cache, (int)cache_rows, 64, box_rows) &&
-                  tc::make_map(&map_v, v_cache, (int)cache_rows, 64, box_rows);
+            tma = tc::make_map(&map_k, k_cache, (int)cache_rows, d, box_rows) &&
+                  tc::make_map(&map_v, v_cache, (int)cache_rows, d, box_rows);
         }
 #define LAUNCH_MMA(DD, NS, TM)                                                                         \
     do {                                                                                               \
@@ -823,6 +834,9 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
             if (stages >= 4) LAUNCH_MMA(64, 4, false);
             else if (stages == 3) LAUNCH_MMA(64, 3, false);
             else LAUNCH_MMA(64, 2, false);
+        } else if (tma) {
+            if (stages >= 3) LAUNCH_MMA(128, 3, true);
+            else LAUNCH_MMA(128, 2, true);
         } else {
             if (stages >= 3) LAUNCH_MMA(128, 3, false);
             else LAUNCH_MMA(128, 2, false);

@@ -55,7 +55,7 @@ KERNELS_BF16 = {
     "D": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma",
           "gemm_tcgen05.swiglu4", "stream_gemm.sink", "stream_gemm.scaled", "stream_gemm.scaled.swiglu",
           "rope_cache", "rmsnorm", "rmsnorm.rows", "embedding"],
-    "E": ["attention_prefill.mma", "attention_decode.mma", "attention_decode_qkv.mma", "stream_gemm.sink",
+    "E": ["attention_prefill.mma", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma", "stream_gemm.sink",
           "stream_gemm.scaled"],
     "A": ["attention_generic", "attention_decode.cuda_core"],
 }
