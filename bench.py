@@ -163,8 +163,8 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: 
     """Device-timed decode: B requests, each step one teacher-forced token per request and the
     sampler kernel; the last step's context is `ctx_end`.  Returns (ms per step, launches per step)."""
     import numpy as np
-    from rust_llm_inference_server_b200 import ops
     from rust_llm_inference_server_b200.engine import StepEntry
+    from rust_llm_inference_server_b200.ops import profile
 
     eng = llm.engine
     runner, cache = eng.runner, eng.cache
@@ -195,6 +195,8 @@ def decode_run(llm, B: int, steps: int, warmup: int, ctx_end: int, torch, fill: 
     for i in range(total):
         if i == warmup:
             torch.cuda.synchronize()
+            if profile.enabled:
+                profile.take_report()       # the table covers the timed steps only
             l0 = runner.launches
             start.record()
         logits = runner.step([StepEntry(sid, [int(toks[i, b])], ctx0 + i, [0]) for b, sid in enumerate(ids)])
@@ -498,6 +500,8 @@ def main() -> int:
         toks = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if args.only and args.spans and it == args.warmup:
+            profile.take_report()           # the table covers the timed steps only
         s.record()
         runner.step([StepEntry(sid, toks, 0, [PREFILL_TOKENS - 1])])
         e.record()

@@ -1,13 +1,14 @@
 // Causal flash attention for portions of prompts over the paged cache on the fifth-generation
-// tensor cores (bfloat16, head size 64, an even number of query heads per kv head, page sizes
-// 8 .. 128 that divide 128).  Same contract as attention_prefill.cu (role in the reference: the
+// tensor cores (bfloat16, head sizes 64 and 128, two or more query heads per kv head, page
+// sizes from 8 on that divide a block of keys: 128 keys for head size 64, 64 for head size 128).  Same contract as attention_prefill.cu (role in the reference: the
 // fused `sdpa` call for multi-token segments, crates/model/src/attention.rs:144-157; scores in
 // float32, keys after the query hidden, softmax in float32, attention.rs:204-233), which stays
 // for the other sizes.
 //
 // One CTA = 64 tokens of one request x TWO query heads of one kv head: the 128 rows of the tensor
 // instruction are (head 0, tokens 0..63), (head 1, tokens 0..63), so every key and value tile is
-// used by both heads.  Per block of 128 keys:
+// used by both heads (a group of three heads is a pair and a head that is taken twice, its copy's
+// rows dropped).  Per block of 128 keys:
 //   warp 0, one lane: TMA.  Q once (two 64 x 64 boxes); the block's K and V page by page (a page
 //           of one kv head is a [page_size x 64] box of the cache seen as a 2-D tensor; pages
 //           past the context are asked for past the end of the tensor and arrive as zeros) into
@@ -25,6 +26,13 @@
 //           the warp rescales its rows of O in tensor memory before the next product.
 // Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
 // other's gaps between the phases.
+//
+// Head size 128 is the same kernel with blocks of 64 keys, so that the tiles are as large and two
+// CTAs still fit: a row of Q, K or V is two 128-byte lines, kept as two swizzled sub-tiles of 64
+// columns (the scores' eight k-steps take four from each; for P V the value tile is the MN-major
+// operand 128 wide, its second sub-tile one leading-dimension offset away), S takes 64 columns of
+// tensor memory and O 128, and a thread's row of scores is 64 long.  Per key the tensor work doubles
+// and the exponentials do not, so the softmax weighs half as much.
 //
 // (Measured at 8192 tokens, 32:8 heads, pages of 16: 706 us, 389 TFLOP/s; the mma.sync kernel
 // 1356 us.  One lane issuing a block's sixteen page copies: 972 us whatever the softmax warps did.
@@ -46,19 +54,37 @@ using namespace tc;
 constexpr int TQ = 64;                  // tokens of a CTA
 static_assert(TQ == RLIS_PREFILL_TILE, "the host's tile list is cut for another tile size");
 constexpr int TM = 128;                 // rows of the instruction: two heads x 64 tokens
-constexpr int TN = 128;                 // keys of a block
-constexpr int HD = 64;                  // head size
 constexpr int KV_STAGES = 2;
-constexpr int Q_BYTES = TM * HD * 2;            // 16 KB
-constexpr int KV_TILE_BYTES = TN * HD * 2;      // 16 KB each for K and V
-constexpr int P_BYTES = TM * TN * 2;            // 32 KB: two [128 x 64] swizzled halves
 constexpr int PT_THREADS = 192;
-// 112 KB of tiles + the control block; with the kilobyte the system keeps per CTA, two CTAs fit the
-// 228 KB of an SM only if no alignment slack is spent: the dynamic array is declared 1024-aligned
-constexpr size_t PT_SMEM = Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES + 128;
-constexpr uint32_t TMEM_COLS = 256;             // S: columns 0..127, O_j: 128..191
-constexpr uint32_t IDESC_S = idesc_bf16(TM, TN);
-constexpr uint32_t IDESC_PV = idesc_bf16(TM, HD) | (1u << 16);      // B (V) is MN-major
+constexpr int LINE_TILE = TM * 128;     // bytes of a swizzled sub-tile of 128 rows: 64 columns, 128-byte lines
+constexpr uint32_t TMEM_COLS = 256;     // S: columns 0 .. TN - 1, O: 128 .. 128 + HD - 1
+
+// Sizes by head size HD and keys of a block TN (64, 128) or (128, 64): 112 KB of tiles either way.
+template <int HD, int TN> struct PShape {
+    static constexpr int Q_BYTES = TM * HD * 2;             // 16 or 32 KB: HD / 64 sub-tiles [128 x 64]
+    static constexpr int KV_TILE_BYTES = TN * HD * 2;       // 16 KB each for K and V: HD / 64 sub-tiles [TN x 64]
+    static constexpr int KV_LINE_TILE = TN * 128;           // bytes of one such sub-tile
+    static constexpr int P_BYTES = TM * TN * 2;             // 32 or 16 KB: TN / 64 sub-tiles [128 x 64]
+    // the tiles + the control block; with the kilobyte the system keeps per CTA, two CTAs fit the
+    // 228 KB of an SM only if no alignment slack is spent: the dynamic array is declared 1024-aligned
+    static constexpr size_t SMEM = Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES + 128;
+    static constexpr uint32_t IDESC_S = idesc_bf16(TM, TN);
+    static constexpr uint32_t IDESC_PV = idesc_bf16(TM, HD) | (1u << 16);      // B (V) is MN-major
+    static constexpr int ROW_F = HD + 4;                    // floats a row in the clusters' exchange area
+    static constexpr int MAX_SPLITS = HD == 64 ? 4 : 2;     // what that area holds: (splits - 1) * 128 rows
+    static_assert((MAX_SPLITS - 1) * TM * ROW_F * 4 <= Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES,
+                  "the exchange area of the cluster merge does not fit the tiles");
+    static_assert(TN == 64 || TN == 128, "a block of keys is one or two swizzled sub-tiles of P");
+    static_assert(TN + 0 <= 128 && HD <= 128, "S and O share 256 columns of tensor memory");
+};
+
+// Shared-memory descriptor of the MN-major operand V under the 128-byte swizzle: lines of 64 head
+// dimensions, 8 keys to a 1024-byte group (the stride field), and, for heads wider than 64, the
+// next 64 dimensions `lbo_bytes` further (the leading-dimension field).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(const void* tile, uint32_t lbo_bytes) {
+    const uint64_t addr = (uint64_t)(smem_u32(tile) >> 4) & 0x3FFFull;
+    return addr | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
 
 struct PCtrl {
     uint64_t q_full;
@@ -106,7 +132,7 @@ __device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int
         lsum += __low2float(h) + __high2float(h);
         pk[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
-    unsigned char* half = prow + (size_t)(c / 2) * (P_BYTES / 2);
+    unsigned char* half = prow + (size_t)(c / 2) * LINE_TILE;
 #pragma unroll
     for (int ch = 0; ch < 4; ++ch) {
         const int chunk = (c % 2) * 4 + ch;
@@ -128,6 +154,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], float inv, 
     }
 }
 // A row of the accumulated output from tensor memory, normalised, to `orow`.
+template <int HD>
 __device__ __forceinline__ void store_row(uint32_t tmem_row, float inv, bool pred, bf16* orow) {
 #pragma unroll 1
     for (int c = 0; c < HD / 32; ++c) {
@@ -142,6 +169,7 @@ __device__ __forceinline__ void store_row(uint32_t tmem_row, float inv, bool pre
 // take, and the rescaling of O in tensor memory becomes rare after the first blocks.
 constexpr float RESCALE_AFTER = 8.0f;
 
+template <int HD, int TN>
 __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
@@ -153,6 +181,10 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         if (threadIdx.x == 0) atomicExch(&g_tc_error, 2);
         return;
     }
+    using SH = PShape<HD, TN>;
+    constexpr int Q_BYTES = SH::Q_BYTES, KV_TILE_BYTES = SH::KV_TILE_BYTES, P_BYTES = SH::P_BYTES;
+    constexpr int KV_LINE_TILE = SH::KV_LINE_TILE;
+    constexpr int HALVES = HD / 64;                                   // sub-tiles of 64 columns in a row of Q, K, V
     unsigned char* q_tile = pt_smem_raw;
     unsigned char* kv_tiles = q_tile + Q_BYTES;                       // [stage][K|V]
     unsigned char* p_tile = kv_tiles + KV_STAGES * 2 * KV_TILE_BYTES;
@@ -160,11 +192,17 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nrep = nh / nkv;
-    // x: the pair of heads, y: the tile; CTAs start in the order of the tile list across all heads
+    // x: the pair of heads, y: the tile; CTAs start in the order of the tile list across all heads.
+    // The query heads of a kv head go in pairs; with an odd number the last pair holds its one head
+    // twice, and the copy's rows are not stored.
     const int b = tiles[2 * blockIdx.y], t0 = tiles[2 * blockIdx.y + 1];
-    const int head0 = (blockIdx.x / splits) * 2;
+    const int pairs = (nrep + 1) / 2;
+    const int pidx = blockIdx.x / splits;
+    const int kvh = pidx / pairs;
+    const int head0 = kvh * nrep + (pidx % pairs) * 2;
+    const bool two = (pidx % pairs) * 2 + 1 < nrep;
+    const int head1 = two ? head0 + 1 : head0;
     const int rank = blockIdx.x % splits;                    // of this CTA in its cluster: it takes blocks rank, rank + splits, ...
-    const int kvh = head0 / nrep;
     const int q_start = cu_seqlens[b];
     const int q_len = cu_seqlens[b + 1] - q_start;
     const int ctx = ctx_lens[b];
@@ -215,11 +253,15 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         // copies of 2 KB a block was what bounded the kernel).
         if (lane == 0) {
             bar_expect_tx(&ctrl->q_full, Q_BYTES);
-            tma_load_2d(q_tile, &map_q, head0 * HD, q_start + t0, &ctrl->q_full);
-            tma_load_2d(q_tile + Q_BYTES / 2, &map_q, (head0 + 1) * HD, q_start + t0, &ctrl->q_full);
+#pragma unroll
+            for (int hf = 0; hf < HALVES; ++hf) {        // sub-tile hf: rows 0..63 head 0, rows 64..127 head 1
+                tma_load_2d(q_tile + hf * LINE_TILE, &map_q, head0 * HD + hf * 64, q_start + t0, &ctrl->q_full);
+                tma_load_2d(q_tile + hf * LINE_TILE + LINE_TILE / 2, &map_q, head1 * HD + hf * 64, q_start + t0,
+                            &ctrl->q_full);
+            }
         }
         const int pages_per_blk = TN / page_size;
-        const int page_bytes = page_size * HD * 2;
+        const int page_bytes = page_size * 128;          // of a page's lines in one sub-tile
         // one tile (the keys or the values of block `it`): a page a lane
         auto load_tile = [&](int it, bool is_v) {
             const int s = it % KV_STAGES;
@@ -230,13 +272,14 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             unsigned char* tile = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + (is_v ? KV_TILE_BYTES : 0);
             if (lane == 0) bar_expect_tx(full, KV_TILE_BYTES);
             __syncwarp();
-            if (lane < pages_per_blk) {
-                const int key = (blk0 + it * splits) * TN + lane * page_size;
+            if (lane < pages_per_blk * HALVES) {
+                const int pg = lane % pages_per_blk, hf = lane / pages_per_blk;
+                const int key = (blk0 + it * splits) * TN + pg * page_size;
                 // a page past the context, or wholly behind the window of the tile's first token
                 // (it may have been given back): a coordinate past the end of the tensor, zeros arrive
                 const bool wanted = key < ctx && (window <= 0 || key + page_size > pos0 - window + 1);
                 const int row = wanted ? (table[key / page_size] * nkv + kvh) * page_size : cache_rows;
-                tma_load_2d(tile + (size_t)lane * page_bytes, is_v ? &map_v : &map_k, 0, row, full);
+                tma_load_2d(tile + (size_t)hf * KV_LINE_TILE + (size_t)pg * page_bytes, is_v ? &map_v : &map_k, hf * 64, row, full);
             }
             __syncwarp();
             return true;
@@ -250,17 +293,22 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = bar_wait(&ctrl->q_full, 0, &ctrl->abort);
-            const uint64_t qdesc = smem_desc_sw128(q_tile);
+            uint64_t qdesc[HALVES];
+#pragma unroll
+            for (int hf = 0; hf < HALVES; ++hf) qdesc[hf] = smem_desc_sw128(q_tile + hf * LINE_TILE);
             auto issue_s = [&](int it) {
                 const int s = it % KV_STAGES;
                 if (!bar_wait(&ctrl->k_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) return false;
                 // the softmax warps have taken the scores of the block before out of tensor memory
                 if (it > 0 && !bar_wait(&ctrl->s_empty, (it - 1) & 1, &ctrl->abort)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t kdesc = smem_desc_sw128(kv_tiles + (size_t)s * 2 * KV_TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    umma_bf16(tmem_s, qdesc + (uint64_t)(k * 32 >> 4), kdesc + (uint64_t)(k * 32 >> 4), IDESC_S, k != 0 ? 1u : 0u);
+                for (int k = 0; k < HD / 16; ++k) {
+                    // four k-steps of 32 bytes inside a sub-tile of 64 columns, then the next sub-tile
+                    const uint64_t kdesc = smem_desc_sw128(kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + (size_t)(k / 4) * KV_LINE_TILE);
+                    umma_bf16(tmem_s, qdesc[k / 4] + (uint64_t)((k % 4) * 32 >> 4), kdesc + (uint64_t)((k % 4) * 32 >> 4),
+                              SH::IDESC_S, k != 0 ? 1u : 0u);
+                }
                 umma_commit(&ctrl->s_full);
                 umma_commit(&ctrl->k_empty[s]);
                 return true;
@@ -275,10 +323,12 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                 const unsigned char* vt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < TN / 16; ++k) {
-                    // P: two swizzled halves of 64 keys, 32 bytes a step inside a half; V: 16 keys = 2 KB further
-                    const uint64_t pdesc = smem_desc_sw128(p_tile + (size_t)(k / 4) * (P_BYTES / 2)) + (uint64_t)((k % 4) * 32 >> 4);
-                    const uint64_t vdesc = smem_desc_sw128(vt + (size_t)k * 16 * HD * 2);
-                    umma_bf16(tmem_o, pdesc, vdesc, IDESC_PV, (it | k) != 0 ? 1u : 0u);     // O accumulates over the blocks
+                    // P: swizzled sub-tiles of 64 keys, 32 bytes a step inside one; V: 16 keys = 2 KB further
+                    // in each of its sub-tiles of 64 head dimensions
+                    const uint64_t pdesc = smem_desc_sw128(p_tile + (size_t)(k / 4) * LINE_TILE) + (uint64_t)((k % 4) * 32 >> 4);
+                    const uint64_t vdesc = HALVES == 1 ? smem_desc_sw128(vt + (size_t)k * 16 * 128)
+                                                       : smem_desc_sw128_mn(vt + (size_t)k * 16 * 128, (uint32_t)KV_LINE_TILE);
+                    umma_bf16(tmem_o, pdesc, vdesc, SH::IDESC_PV, (it | k) != 0 ? 1u : 0u);     // O accumulates over the blocks
                 }
                 umma_commit(&ctrl->o_full);
                 umma_commit(&ctrl->v_empty[s]);
@@ -298,11 +348,13 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             ok = bar_wait(&ctrl->s_full, it & 1, &ctrl->abort) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // the whole row of scores at once, and tensor memory is free for the next block's scores
-            uint32_t s0[32], s1[32], s2[32], s3[32];
+            uint32_t s0[32], s1[32], s2[TN > 64 ? 32 : 1], s3[TN > 64 ? 32 : 1];
             tmem_ld32_nowait(tmem_s + lane_addr, s0);
             tmem_ld32_nowait(tmem_s + lane_addr + 32u, s1);
-            tmem_ld32_nowait(tmem_s + lane_addr + 64u, s2);
-            tmem_ld32_nowait(tmem_s + lane_addr + 96u, s3);
+            if constexpr (TN > 64) {
+                tmem_ld32_nowait(tmem_s + lane_addr + 64u, s2);
+                tmem_ld32_nowait(tmem_s + lane_addr + 96u, s3);
+            }
             tmem_ld_wait();
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -314,13 +366,17 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             if (need_mask) {
                 max_of_chunk<true>(s0, 0, kmin, kmax, mx);
                 max_of_chunk<true>(s1, 1, kmin, kmax, mx);
-                max_of_chunk<true>(s2, 2, kmin, kmax, mx);
-                max_of_chunk<true>(s3, 3, kmin, kmax, mx);
+                if constexpr (TN > 64) {
+                    max_of_chunk<true>(s2, 2, kmin, kmax, mx);
+                    max_of_chunk<true>(s3, 3, kmin, kmax, mx);
+                }
             } else {
                 max_of_chunk<false>(s0, 0, kmin, kmax, mx);
                 max_of_chunk<false>(s1, 1, kmin, kmax, mx);
-                max_of_chunk<false>(s2, 2, kmin, kmax, mx);
-                max_of_chunk<false>(s3, 3, kmin, kmax, mx);
+                if constexpr (TN > 64) {
+                    max_of_chunk<false>(s2, 2, kmin, kmax, mx);
+                    max_of_chunk<false>(s3, 3, kmin, kmax, mx);
+                }
             }
             const float m_new = fmaxf(m_ref, mx * scale_log2);
             // the reference moves only when the maximum has run ahead of it (always on the first keys seen)
@@ -352,23 +408,31 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             if (need_mask) {
                 exp_of_chunk<true>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
                 exp_of_chunk<true>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<true>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<true>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                if constexpr (TN > 64) {
+                    exp_of_chunk<true>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                    exp_of_chunk<true>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                }
             } else {
                 exp_of_chunk<false>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
                 exp_of_chunk<false>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<false>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<false>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                if constexpr (TN > 64) {
+                    exp_of_chunk<false>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                    exp_of_chunk<false>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
+                }
             }
             l_run += lsum;
             // Slots of the last page past the context hold whatever was there before; a zero of P
             // times a NaN would still be a NaN, so those rows of V are cleared (thread r: key r of
             // the block), once the tile has arrived
             if (key0 + TN > ctx) ok = bar_wait(&ctrl->v_full[it % KV_STAGES], (it / KV_STAGES) & 1, &ctrl->abort) && ok;
-            if (key0 + r >= ctx) {
-                uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES + (size_t)r * 128);
+            if (r < TN && key0 + r >= ctx) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+                for (int hf = 0; hf < HALVES; ++hf) {
+                    uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES +
+                                                           (size_t)hf * KV_LINE_TILE + (size_t)r * 128);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
             // P is in shared memory for the tensor core, O (if rescaled) back in tensor memory
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -383,16 +447,16 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         row_ok = ok;
     }
     // the row's place in the output: head (srow / 64) of the pair, token (srow % 64) of the tile
-    const bool srow_valid = (srow & 63) < n_valid;
-    bf16* sorow = out + ((size_t)(q_start + t0 + (srow & 63)) * nh + head0 + (srow >> 6)) * HD;
+    const bool srow_valid = (srow & 63) < n_valid && (srow < 64 || two);
+    bf16* sorow = out + ((size_t)(q_start + t0 + (srow & 63)) * nh + (srow < 64 ? head0 : head1)) * HD;
     if (splits == 1) {
-        if (warp >= 2 && n_blk > 0) store_row(tmem_o + slane_addr, 1.0f / l_run, row_ok && srow_valid, sorow);
+        if (warp >= 2 && n_blk > 0) store_row<HD>(tmem_o + slane_addr, 1.0f / l_run, row_ok && srow_valid, sorow);
     } else {
         // The CTAs of the cluster took the blocks of keys in turn.  Once all their products are done
         // (the tiles in shared memory are free), ranks 1.. send their rows (64 unnormalised sums,
         // the reference of the exponentials and their sum) into rank 0's tiles; rank 0 brings them
         // to one reference in the order of the ranks, adds, normalises and stores.
-        constexpr int ROW_F = 68;                      // floats a row in the exchange area (16-byte aligned rows)
+        constexpr int ROW_F = SH::ROW_F;               // floats a row in the exchange area (16-byte aligned rows)
         float* xchg = reinterpret_cast<float*>(pt_smem_raw);
         __syncwarp();
         cluster_sync_all();
@@ -495,12 +559,48 @@ extern "C" void rlis_attention_prefill_tc_set_splits(int splits) { g_pf_splits =
 
 // Whether the tensor-core kernel takes these sizes (else the caller uses rlis_attention_prefill).
 extern "C" int rlis_attention_prefill_tc_takes(int nh, int nkv, int d, int page_size) {
-    if (d != HD || nkv <= 0 || nh % nkv != 0 || ((nh / nkv) & 1) != 0) return 0;
-    if (page_size < 8 || page_size > TN || TN % page_size != 0) return 0;
+    if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv != 0 || nh / nkv < 2) return 0;
+    const int tn = d == 64 ? 128 : 64;                  // keys of a block
+    if (page_size < 8 || page_size > tn || tn % page_size != 0) return 0;
     return 1;
 }
 
-// q, out [tokens, nh * 64]; caches [pages, nkv, page_size, 64]; tiles [n_tiles, 2] = (batch entry,
+namespace {
+template <int HD, int TN>
+int launch_prefill_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, bf16* out,
+                      const int* tiles, int n_tiles, const int* cu_seqlens, const int* ctx_lens, const int* block_tables,
+                      int max_blocks, int nh, int nkv, int page_size, int cache_rows, float scale, int window, int max_ctx,
+                      cudaStream_t stream) {
+    using SH = PShape<HD, TN>;
+    const int pairs = nkv * ((nh / nkv + 1) / 2);          // CTAs a tile: the query heads of a kv head in pairs
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SH::SMEM);
+        attr_done = true;
+    }
+    // Few tiles with many keys each (a short portion of a long prompt) would leave SMs idle, and the
+    // tiles at the end of a prompt run long after the others are done: 2 or 4 CTAs of a cluster then
+    // share a tile's blocks of keys.  max_ctx: the longest context of the step (0: unknown, no sharing).
+    int splits = g_pf_splits;
+    if (splits <= 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long ctas = (long long)n_tiles * pairs;
+        const int blocks = window > 0 ? (window + TQ + TN - 1) / TN + 1 : (max_ctx + TN - 1) / TN;
+        splits = 1;
+        // measured: it pays while the CTAs still fit the SMs at once (two each) and every one keeps 8 blocks
+        while (splits < SH::MAX_SPLITS && ctas * splits * 2 <= 2ll * sms && blocks >= 16 * splits) splits *= 2;
+    }
+    if (splits > SH::MAX_SPLITS) splits = SH::MAX_SPLITS;
+    if (splits != 1 && splits != 2 && splits != 4) return RLIS_ERR_UNSUPPORTED;
+    rlis_launch_cluster(attn_prefill_tc_kernel<HD, TN>, dim3((unsigned)(pairs * splits), (unsigned)n_tiles), PT_THREADS,
+                        SH::SMEM, stream, dim3((unsigned)splits, 1, 1), map_q, map_k, map_v, out, tiles, cu_seqlens,
+                        ctx_lens, block_tables, max_blocks, nh, nkv, page_size, cache_rows, scale, window, splits);
+    return RLIS_LAUNCH_CHECK();
+}
+}  // namespace
+
+// q, out [tokens, nh * d]; caches [pages, nkv, page_size, d]; tiles [n_tiles, 2] = (batch entry,
 // first token of 64) as for rlis_attention_prefill; max_ctx: the longest context among the
 // requests of the step, or 0.
 extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -517,31 +617,13 @@ extern "C" int rlis_attention_prefill_tc(const void* q, const void* k_cache, con
     const long long cache_rows = (long long)n_pages * nkv * page_size;
     if (cache_rows >= (1ll << 31)) return RLIS_ERR_UNSUPPORTED;
     CUtensorMap map_q, map_k, map_v;
-    if (!make_map_2d(&map_q, q, n_tokens, (long long)nh * HD, TQ) ||
-        !make_map_2d(&map_k, k_cache, cache_rows, HD, page_size) ||
-        !make_map_2d(&map_v, v_cache, cache_rows, HD, page_size))
+    if (!make_map_2d(&map_q, q, n_tokens, (long long)nh * d, TQ) ||
+        !make_map_2d(&map_k, k_cache, cache_rows, d, page_size) ||
+        !make_map_2d(&map_v, v_cache, cache_rows, d, page_size))
         return RLIS_ERR_UNSUPPORTED;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PT_SMEM);
-        attr_done = true;
-    }
-    // Few tiles with many keys each (a short portion of a long prompt) would leave SMs idle, and the
-    // tiles at the end of a prompt run long after the others are done: 2 or 4 CTAs of a cluster then
-    // share a tile's blocks of keys.  max_ctx: the longest context of the step (0: unknown, no sharing).
-    int splits = g_pf_splits;
-    if (splits <= 0) {
-        int dev = 0, sms = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const long long ctas = (long long)n_tiles * (nh / 2);
-        const int blocks = window > 0 ? (window + TQ + TN - 1) / TN + 1 : (max_ctx + TN - 1) / TN;
-        splits = 1;
-        // measured: it pays while the CTAs still fit the SMs at once (two each) and every one keeps 8 blocks
-        while (splits < 4 && ctas * splits * 2 <= 2ll * sms && blocks >= 16 * splits) splits *= 2;
-    }
-    if (splits != 1 && splits != 2 && splits != 4) return RLIS_ERR_UNSUPPORTED;
-    rlis_launch_cluster(attn_prefill_tc_kernel, dim3((unsigned)(nh / 2 * splits), (unsigned)n_tiles), PT_THREADS, PT_SMEM,
-                        stream, dim3((unsigned)splits, 1, 1), map_q, map_k, map_v, (bf16*)out, tiles, cu_seqlens,
-                        ctx_lens, block_tables, max_blocks, nh, nkv, page_size, (int)cache_rows, scale, window, splits);
-    return RLIS_LAUNCH_CHECK();
+    if (d == 64)
+        return launch_prefill_tc<64, 128>(map_q, map_k, map_v, (bf16*)out, tiles, n_tiles, cu_seqlens, ctx_lens, block_tables,
+                                          max_blocks, nh, nkv, page_size, (int)cache_rows, scale, window, max_ctx, stream);
+    return launch_prefill_tc<128, 64>(map_q, map_k, map_v, (bf16*)out, tiles, n_tiles, cu_seqlens, ctx_lens, block_tables,
+                                      max_blocks, nh, nkv, page_size, (int)cache_rows, scale, window, max_ctx, stream);
 }

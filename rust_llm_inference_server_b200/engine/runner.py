@@ -10,6 +10,7 @@ of all index arrays per step.
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -21,6 +22,10 @@ from ..ops import profile
 
 class StepError(ValueError):
     """A batch the step function refuses before anything is launched."""
+
+
+class _CaptureAbort(Exception):
+    """A scratch buffer would have to grow while a graph is being recorded."""
 
 
 @dataclass
@@ -108,6 +113,7 @@ class ModelRunner:
         self._graph_pool = None
         self._upload_done = None
         self._graph_launches = 0
+        self._capturing = False
 
     # ---- scratch memory that keeps its address while it is large enough ----
 
@@ -117,6 +123,10 @@ class ModelRunner:
             n *= int(s)
         buf = self._ws.get(name)
         if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if self._capturing:
+                # (graphs cannot be dropped while one is being recorded; the step runs eagerly instead,
+                # which sizes the buffer, and the shape is captured the next time it comes)
+                raise _CaptureAbort(name)
             cap = max(n, 2 * buf.numel() if buf is not None and buf.dtype == dtype else n)
             self._drop_graphs()         # captured graphs point at the old buffer
             buf = torch.empty((cap,), dtype=dtype, device=self.device)
@@ -307,21 +317,43 @@ class ModelRunner:
             if seen < self.GRAPH_AFTER_STEPS:
                 self._graph_seen[key] = seen + 1
                 return self._forward_eager(st)
-            before = ops.launch_count
-            graph = torch.cuda.CUDAGraph()
-            if self._graph_pool is None:
-                self._graph_pool = torch.cuda.graph_pool_handle()
-            torch.cuda.synchronize()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                logits = self._forward_eager(st)
-            n = ops.launch_count - before
-            ops.launch_count = before           # capturing launches nothing
-            entry = (graph, logits, n)
+            entry = self._capture(st)
+            if entry is None:                   # not this time: the step runs as it is
+                return self._forward_eager(st)
             self._graphs[key] = entry
         graph, logits, n = entry
         graph.replay()
         self._graph_launches += n
         return logits
+
+    def _capture(self, st: StepContext):
+        """Records the step into a CUDA graph: (graph, its logits buffer, launches it holds), or None
+        when the recording had to be given up.  While a stream records, freeing device memory or
+        another graph is not allowed, and Python's collector may do just that when it meets a dead
+        engine: it is held off for the duration."""
+        before = ops.launch_count
+        counts = dict(ops.launches_by_kernel)
+        graph = torch.cuda.CUDAGraph()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        torch.cuda.synchronize()
+        collecting = gc.isenabled()
+        gc.disable()
+        self._capturing = True
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self._forward_eager(st)
+        except _CaptureAbort:
+            return None
+        finally:
+            self._capturing = False
+            if collecting:
+                gc.enable()
+            n = ops.launch_count - before
+            ops.launch_count = before           # recording launches nothing
+            ops.launches_by_kernel.clear()
+            ops.launches_by_kernel.update(counts)
+        return graph, logits, n
 
     def step(self, entries: list):
         return self.forward(self.prepare(entries))

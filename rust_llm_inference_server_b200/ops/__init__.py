@@ -528,7 +528,7 @@ def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, blo
     if head_dim not in (64, 128) or n_heads % n_kv_heads:
         raise KernelError(f"prefill attention: head size {head_dim} is not taken (64 and 128 are)")
     if PREFILL_TCGEN05 and lib().rlis_attention_prefill_tc_takes(n_heads, n_kv_heads, head_dim, page_size):
-        # the tcgen05 kernel: head size 64, query heads in pairs, pages that divide a block of 128 keys
+        # the tcgen05 kernel: head sizes 64 and 128, two or more query heads a kv head, pages that divide a block of keys
         check(lib().rlis_attention_prefill_tc(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), tiles.data_ptr(),
             tiles.shape[0], cu_seqlens.data_ptr(), ctx_lens.data_ptr(), block_tables.data_ptr(),

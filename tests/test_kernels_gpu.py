@@ -387,7 +387,9 @@ def test_decode_attention_split_over_the_context(geom, ps, splits):
 
 
 @pytest.mark.parametrize("geom,ps", [((32, 8, 64), 16), ((6, 3, 128), 16), ((4, 4, 64), 8), ((5, 1, 128), 32),
-                                     ((8, 2, 64), 8), ((4, 1, 64), 32), ((12, 6, 64), 128), ((6, 1, 64), 64)])
+                                     ((8, 2, 64), 8), ((4, 1, 64), 32), ((12, 6, 64), 128), ((6, 1, 64), 64),
+                                     ((8, 2, 128), 16), ((24, 8, 128), 8), ((4, 2, 128), 64), ((2, 1, 128), 32),
+                                     ((4, 2, 128), 128), ((9, 3, 64), 16), ((5, 1, 64), 8), ((24, 8, 128), 16)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_prefill_flash_attention_over_pages(geom, ps, window):
     """Portions of prompts of many lengths (one token short of a tile, exactly a tile, across
@@ -416,9 +418,11 @@ def test_prefill_flash_attention_over_pages(geom, ps, window):
     ops.check_device_errors()
 
 
-def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
+@pytest.mark.parametrize("geom", [(8, 2, 64), (4, 1, 128)])
+def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge(geom):
     from rust_llm_inference_server_b200 import ops
-    geom, ps = (8, 2, 64), 16
+    ps = 16
+    nh, nkv, d = geom
     n, m = 1000, 200           # the last 200 tokens are queries
     cu = torch.tensor([0, m], dtype=torch.int32)
     tiles = torch.tensor([(0, t0) for t0 in range(0, m, 64)], dtype=torch.int32)
@@ -428,13 +432,14 @@ def test_prefill_flash_attention_finds_far_keys_and_the_causal_edge():
         # few tiles and a long context: the kernel shares each tile's keys among the CTAs of a cluster
         out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
         ops.attention_prefill(dev(q), dev(kc), dev(vc), out, dev(tiles), dev(cu), dev(torch.tensor([n], dtype=torch.int32)),
-                              dev(tables), 8, 2, 64, ps, 0.125, 0, n)
-        got = out.float().cpu().view(m, 8, 64)
+                              dev(tables), nh, nkv, d, ps, 1 / math.sqrt(d), 0, n)
+        got = out.float().cpu().view(m, nh, d)
         assert (got - want).abs().max() <= 3e-2
         assert ((got[qi] - 7.0).abs().max() < 0.05) == seen, (qi, key)
 
 
-@pytest.mark.parametrize("geom,tcgen05", [((8, 2, 64), True), ((8, 2, 64), False), ((6, 3, 128), False), ((4, 4, 64), False)])
+@pytest.mark.parametrize("geom,tcgen05", [((8, 2, 64), True), ((8, 2, 64), False), ((6, 3, 128), False), ((4, 4, 64), False),
+                                          ((4, 2, 128), True), ((4, 2, 128), False)])
 @pytest.mark.parametrize("W", [70, 129])
 def test_prefill_flash_attention_window_edge(geom, tcgen05, W):
     """With a window of W keys, the query at position p sees the key at p - W + 1 and not the one at

@@ -55,7 +55,7 @@ KERNELS_BF16 = {
     "D": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma",
           "gemm_tcgen05.swiglu4", "stream_gemm.sink", "stream_gemm.scaled", "stream_gemm.scaled.swiglu",
           "rope_cache", "rmsnorm", "rmsnorm.rows", "embedding"],
-    "E": ["attention_prefill.mma", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma", "stream_gemm.sink",
+    "E": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma", "stream_gemm.sink",
           "stream_gemm.scaled"],
     "A": ["attention_generic", "attention_decode.cuda_core"],
 }
@@ -73,7 +73,8 @@ def compare(got: dict, ref: dict, tol: float, what: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which,page", [("A", 16), ("A", 8), ("B", 16), ("C", 16), ("D", 16), ("D", 32), ("E", 16), ("E", 64)])
+@pytest.mark.parametrize("which,page", [("A", 16), ("A", 8), ("B", 16), ("C", 16), ("D", 16), ("D", 32), ("E", 16), ("E", 64),
+                                        ("E", 128)])
 def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, dtype):
     from rust_llm_inference_server_b200 import ops
     ops.launches_by_kernel.clear()
@@ -88,7 +89,7 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, dtyp
     }
     results = {}
     for fam, steps in families.items():
-        s = session(model_root, which, dtype, R.live_token_peak(steps), page)   # the smallest pool allowed
+        s = session(model_root, which, dtype, R.live_token_peak(steps, max(64, page)), page)   # the smallest pool allowed
         results[fam] = R.collect(s.step, steps)
         if dtype == "bfloat16" and fam == "decode" and which in ("D", "E"):
             assert s.runner._graph_launches > 0            # single tokens ran from captured graphs
@@ -101,7 +102,10 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, dtyp
         worst = max(float(np.abs(v - whole[k]).max()) for k, v in sub.items())
         assert worst <= TOL_BETWEEN_MODES[dtype], f"{which} {dtype}: {fam} differs from whole by {worst}"
     if dtype == "bfloat16":
-        missing = [k for k in KERNELS_BF16.get(which, []) if not ops.launches_by_kernel.get(k)]
+        expected = list(KERNELS_BF16.get(which, []))
+        if (which, page) == ("E", 128):      # a page larger than the tcgen05 kernel's block of 64 keys: the mma.sync kernel
+            expected[expected.index("attention_prefill.tcgen05")] = "attention_prefill.mma"
+        missing = [k for k in expected if not ops.launches_by_kernel.get(k)]
         assert not missing, f"{which}: never launched {missing}; launched {sorted(ops.launches_by_kernel)}"
     else:
         fast = [k for k in ops.launches_by_kernel if "tcgen05" in k or "mma" in k or "stream_gemm" in k]
