@@ -47,13 +47,31 @@ def plan_groups(slot_specs, page_size: int) -> list[CacheGroup]:
     return groups
 
 
-def size_groups(groups: list[CacheGroup], kv_cache_bytes: int, elem_size: int) -> None:
-    """Every group gets the same number of pages, as many as `kv_cache_bytes` pays for
-    (crates/model/src/paged.rs:109-116 for the single-group case)."""
+def size_groups(groups: list[CacheGroup], kv_cache_bytes: int, elem_size: int,
+                max_num_seqs: int | None = None, max_batched_tokens: int | None = None) -> None:
+    """Pages for every group out of `kv_cache_bytes`: the same number each
+    (crates/model/src/paged.rs:109-116 for the single-group case), except that a window group is
+    not given more than its requests can ever hold at once (a window plus one portion of a prompt,
+    and the page either end may straddle, per seat); what that saves goes to the groups that keep
+    every token."""
     per_page = sum(g.bytes_per_page(elem_size) for g in groups)
     n = kv_cache_bytes // per_page if per_page else 0
     for g in groups:
         g.num_pages = int(n)
+    if not max_num_seqs or not max_batched_tokens:
+        return
+    saved = 0
+    for g in groups:
+        if g.window:
+            most = max_num_seqs * (-(-(g.window + max_batched_tokens) // g.page_size) + 2)
+            if g.num_pages > most:
+                saved += (g.num_pages - most) * g.bytes_per_page(elem_size)
+                g.num_pages = most
+    keep_all = [g for g in groups if not g.window]
+    if keep_all and saved:
+        extra = saved // sum(g.bytes_per_page(elem_size) for g in keep_all)
+        for g in keep_all:
+            g.num_pages += int(extra)
 
 
 class CacheStorage:

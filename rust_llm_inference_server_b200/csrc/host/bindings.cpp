@@ -123,6 +123,10 @@ PYBIND11_MODULE(_rlis_host, m) {
         .def("watermark", &CacheManager::watermark)
         .def("set_watermark", &CacheManager::set_watermark)
         .def("max_seq_tokens", &CacheManager::max_seq_tokens)
+        .def("admit", [](CacheManager& c, SeqId seq, const std::vector<int32_t>& tokens, size_t portion_tokens, bool use_prefix) {
+            CacheManager::Admission a = c.admit(seq, tokens.data(), tokens.size(), portion_tokens, use_prefix);
+            return py::make_tuple(a.ok, a.cached_pages);
+        }, py::arg("seq"), py::arg("tokens"), py::arg("portion_tokens"), py::arg("use_prefix") = true)
         .def("adopt_prefix", &CacheManager::adopt_prefix)
         .def("register_page", &CacheManager::register_page)
         .def("check_invariants", &CacheManager::check_invariants)

@@ -1,17 +1,17 @@
 // Paged cache bookkeeping: which physical pages hold which request's tokens.  Host logic only;
 // the tensors live on the device and are addressed by the page ids handed out here.
 //
-// What it does, after crates/kvcache/src/lib.rs of akshajnad/rust_llm_inference_server
-// (free list, reference counts, hashed-page prefix reuse with least-recently-freed reclaim,
-// all-or-nothing reservation, invariants check), re-designed around *groups*: layers with the
-// same cache needs (geometry, keep-all or a window) share one pool of pages and one block table
-// per request.  A window group gives pages back once every later query has passed them.  Beside
-// the pages sits a pool of fixed-size per-request state slots.
+// It keeps the behaviour of crates/kvcache/src/lib.rs of akshajnad/rust_llm_inference_server
+// (pages reused last-returned-first, counted holders, full pages found again by the hash of their
+// prefix and recycled oldest first, all-or-nothing reservation, a consistency check) in a design
+// of its own, built around *groups*: layers with the same cache needs (geometry, keep-all or a
+// window) share one pool of pages and one block table per request.  A window group gives pages
+// back once every later query has passed them.  Beside the pages sits a pool of fixed-size
+// per-request state slots, and admission of a request is one transaction over all of them.
 #pragma once
 
 #include <algorithm>
 #include <cstdint>
-#include <map>
 #include <sstream>
 #include <stdexcept>
 #include <string>
@@ -58,113 +58,143 @@ inline std::vector<uint64_t> page_hashes(const int32_t* tokens, size_t n_tokens,
     return out;
 }
 
-// One group's pages: free list (last in, first out), reference counts, and the registry of
-// full pages by content hash.  A registered page whose count falls to zero stays cached
-// ("evictable") and is reclaimed, oldest first, only when the free list is empty.
+// The pages of one group.  Every page is in exactly one of three places:
+//   held   one or more requests have it in their tables (`holders` counts them);
+//   kept   nobody holds it, but it is full and known by the hash of the tokens up to its end: it
+//          sits in the keep-list, a doubly linked list threaded through the page records, newest
+//          at the tail, from where a request with the same prefix can take it back;
+//   blank  on the blank stack; the page returned last is handed out first.
+// A page is handed out from the blank stack while that has any; only then is the head of the
+// keep-list (the page nobody has wanted for longest) stripped of its name and reused.
+// Behaviour after crates/kvcache/src/lib.rs:57-166 (free list, reference counts, evictable cached
+// blocks reclaimed least-recently-freed first).
 class PagePool {
 public:
-    explicit PagePool(int num_pages)
-        : refcount_(num_pages, 0), has_hash_(num_pages, 0), hash_of_(num_pages, 0),
-          evict_tick_(num_pages, 0) {
-        free_.reserve(num_pages);
-        for (int b = num_pages - 1; b >= 0; --b) free_.push_back(b);
+    explicit PagePool(int num_pages) : page_(num_pages) {
+        blank_.reserve(num_pages);
+        for (int b = num_pages - 1; b >= 0; --b) blank_.push_back(b);   // page 0 goes out first
     }
 
-    int num_pages() const { return static_cast<int>(refcount_.size()); }
-    int num_free() const { return static_cast<int>(free_.size() + evictable_.size()); }
-    int num_evictable() const { return static_cast<int>(evictable_.size()); }
-    uint32_t refcount(PageId b) const { return refcount_.at(b); }
+    int num_pages() const { return static_cast<int>(page_.size()); }
+    int num_free() const { return static_cast<int>(blank_.size()) + kept_; }   // what a reservation can draw on
+    int num_evictable() const { return kept_; }
+    uint32_t refcount(PageId b) const { return page_.at(b).holders; }
 
-    PageId lookup(uint64_t hash) const {
-        auto it = cached_.find(hash);
-        return it == cached_.end() ? kNoPage : it->second;
+    PageId lookup(uint64_t name) const {
+        auto it = by_name_.find(name);
+        return it == by_name_.end() ? kNoPage : it->second;
     }
 
-    // First writer wins: a second page with the same content stays unregistered.
-    void register_page(PageId b, uint64_t hash) {
-        if (!has_hash_[b] && cached_.find(hash) == cached_.end()) {
-            has_hash_[b] = 1;
-            hash_of_[b] = hash;
-            cached_[hash] = b;
-        }
+    // Gives page b its name.  A page keeps the first name it gets, and a name the first page that
+    // takes it: a second page with the same contents stays anonymous.
+    void register_page(PageId b, uint64_t name) {
+        Page& pg = page_.at(b);
+        if (pg.named || by_name_.count(name)) return;
+        pg.named = true;
+        pg.name = name;
+        by_name_.emplace(name, b);
     }
 
-    // Takes a reference to a registered page, reviving it if it was evictable.
+    // One more holder of a named page; if it was waiting in the keep-list it leaves it.
     void acquire(PageId b) {
-        if (evict_tick_[b] != 0) {
-            evictable_.erase(evict_tick_[b]);
-            evict_tick_[b] = 0;
+        Page& pg = page_.at(b);
+        if (pg.holders == 0) {
+            if (!pg.in_keep) throw std::logic_error("acquired a page that is neither held nor kept");
+            unlink(b);
         }
-        ++refcount_[b];
+        ++pg.holders;
     }
 
     PageId allocate() {
         PageId b;
-        if (!free_.empty()) {
-            b = free_.back();
-            free_.pop_back();
-        } else if (!evictable_.empty()) {
-            auto it = evictable_.begin();
-            b = it->second;
-            evictable_.erase(it);
-            evict_tick_[b] = 0;
-            cached_.erase(hash_of_[b]);
-            has_hash_[b] = 0;
+        if (!blank_.empty()) {
+            b = blank_.back();
+            blank_.pop_back();
+        } else if (keep_head_ != kNoPage) {
+            b = keep_head_;
+            unlink(b);
+            by_name_.erase(page_[b].name);
+            page_[b].named = false;
         } else {
             return kNoPage;
         }
-        if (refcount_[b] != 0) throw std::logic_error("allocated a page that is still referenced");
-        refcount_[b] = 1;
+        if (page_[b].holders != 0) throw std::logic_error("handed out a page that is still held");
+        page_[b].holders = 1;
         return b;
     }
 
     void decref(PageId b) {
-        if (refcount_.at(b) == 0) throw std::logic_error("page " + std::to_string(b) + " freed twice");
-        if (--refcount_[b] == 0) {
-            if (has_hash_[b]) {
-                evict_tick_[b] = ++tick_;
-                evictable_[tick_] = b;
-            } else {
-                free_.push_back(b);
-            }
-        }
+        Page& pg = page_.at(b);
+        if (pg.holders == 0) throw std::logic_error("page " + std::to_string(b) + " freed twice");
+        if (--pg.holders != 0) return;
+        if (pg.named) append(b);
+        else blank_.push_back(b);
     }
 
-    // Consistency of the pool with `holders[b]` = number of tables that hold page b.
+    // Consistency with `holders[b]`, the number of tables that hold page b; empty when fine.
     std::string check(const std::vector<uint32_t>& holders) const {
         const int n = num_pages();
-        std::vector<char> in_free(n, 0);
+        std::vector<char> idle(n, 0);
         std::ostringstream err;
-        for (PageId b : free_) {
-            if (in_free[b]++) { err << "page " << b << " is on the free list twice"; return err.str(); }
-            if (has_hash_[b]) { err << "free page " << b << " is still registered"; return err.str(); }
+        for (PageId b : blank_) {
+            if (idle[b]++) { err << "page " << b << " is on the blank stack twice"; return err.str(); }
+            if (page_[b].named || page_[b].in_keep) { err << "blank page " << b << " still has a name"; return err.str(); }
         }
-        for (auto& kv : evictable_) {
-            PageId b = kv.second;
-            if (in_free[b]++) { err << "page " << b << " is both free and evictable"; return err.str(); }
-            if (evict_tick_[b] != kv.first || !has_hash_[b]) { err << "evictable page " << b << " has stale bookkeeping"; return err.str(); }
+        int walked = 0;
+        PageId before = kNoPage;
+        for (PageId b = keep_head_; b != kNoPage; before = b, b = page_[b].next) {
+            if (++walked > n) return "the keep-list has a loop";
+            if (idle[b]++) { err << "page " << b << " is both blank and kept, or kept twice"; return err.str(); }
+            if (!page_[b].named || !page_[b].in_keep || page_[b].prev != before) { err << "kept page " << b << " has stale links"; return err.str(); }
         }
-        size_t registered = 0;
-        for (int b = 0; b < n; ++b) registered += has_hash_[b] ? 1 : 0;
-        if (registered != cached_.size()) return "registered pages and cache entries disagree";
-        for (auto& kv : cached_)
-            if (!has_hash_[kv.second] || hash_of_[kv.second] != kv.first) { err << "cache entry points at page " << kv.second << " with another hash"; return err.str(); }
+        if (before != keep_tail_ || walked != kept_) return "the keep-list and its counters disagree";
+        size_t named = 0;
+        for (int b = 0; b < n; ++b) named += page_[b].named ? 1 : 0;
+        if (named != by_name_.size()) return "named pages and the name index disagree";
+        for (auto& kv : by_name_)
+            if (!page_[kv.second].named || page_[kv.second].name != kv.first) { err << "the name index points at page " << kv.second << " with another name"; return err.str(); }
         for (int b = 0; b < n; ++b) {
-            if (refcount_[b] != holders[b]) { err << "page " << b << ": count " << refcount_[b] << " but " << holders[b] << " tables hold it"; return err.str(); }
-            if ((refcount_[b] == 0) != (in_free[b] != 0)) { err << "page " << b << ": count " << refcount_[b] << ", free or evictable: " << int(in_free[b]); return err.str(); }
+            if (page_[b].holders != holders[b]) { err << "page " << b << ": " << page_[b].holders << " holders recorded but " << holders[b] << " tables hold it"; return err.str(); }
+            if ((page_[b].holders == 0) != (idle[b] != 0)) { err << "page " << b << ": " << page_[b].holders << " holders, blank or kept: " << int(idle[b]); return err.str(); }
         }
         return "";
     }
 
 private:
-    std::vector<uint32_t> refcount_;
-    std::vector<PageId> free_;
-    std::vector<char> has_hash_;
-    std::vector<uint64_t> hash_of_;
-    std::unordered_map<uint64_t, PageId> cached_;
-    std::map<uint64_t, PageId> evictable_;  // by tick of the last release, oldest first
-    std::vector<uint64_t> evict_tick_;      // 0 = not evictable
-    uint64_t tick_ = 0;
+    struct Page {
+        uint32_t holders = 0;
+        bool named = false, in_keep = false;
+        uint64_t name = 0;
+        PageId prev = kNoPage, next = kNoPage;    // neighbours in the keep-list
+    };
+
+    void append(PageId b) {
+        Page& pg = page_[b];
+        pg.prev = keep_tail_;
+        pg.next = kNoPage;
+        pg.in_keep = true;
+        if (keep_tail_ != kNoPage) page_[keep_tail_].next = b;
+        else keep_head_ = b;
+        keep_tail_ = b;
+        ++kept_;
+    }
+
+    void unlink(PageId b) {
+        Page& pg = page_[b];
+        if (pg.prev != kNoPage) page_[pg.prev].next = pg.next;
+        else keep_head_ = pg.next;
+        if (pg.next != kNoPage) page_[pg.next].prev = pg.prev;
+        else keep_tail_ = pg.prev;
+        pg.prev = pg.next = kNoPage;
+        pg.in_keep = false;
+        --kept_;
+    }
+
+    std::vector<Page> page_;
+    std::vector<PageId> blank_;
+    std::unordered_map<uint64_t, PageId> by_name_;
+    PageId keep_head_ = kNoPage, keep_tail_ = kNoPage;
+    int kept_ = 0;
 };
 
 // A request's logical-to-physical map in one group: token i lives in pages[i / page_size] at
@@ -345,12 +375,12 @@ public:
     }
 
     // Whether a request of `num_tokens` tokens whose first `matched` pages are cached fits now,
-    // leaving `watermark(g)` pages free in every group.  Window groups are asked for
-    // `window_tokens` tokens only (what the next portion can need), not for the whole request.
-    bool fits(size_t num_tokens, size_t window_tokens, size_t matched,
+    // leaving `watermark(g)` pages free in every group.  A window group is asked for what the
+    // request can hold there at once: its window plus one portion of `portion_tokens`.
+    bool fits(size_t num_tokens, size_t portion_tokens, size_t matched,
               const std::vector<int>& matched_evictable) const {
         for (size_t g = 0; g < groups_.size(); ++g) {
-            const size_t toks = groups_[g].window ? std::min(num_tokens, window_tokens) : num_tokens;
+            const size_t toks = groups_[g].window ? std::min(num_tokens, size_t(groups_[g].window) + portion_tokens) : num_tokens;
             const size_t need = pages_for(int(g), toks) - std::min(matched, pages_for(int(g), toks));
             const long avail = long(pools_[g].num_free()) - (g < matched_evictable.size() ? matched_evictable[g] : 0);
             if (long(need) + long(watermark(int(g))) > avail) return false;
@@ -373,6 +403,38 @@ public:
             best = std::min(best, size_t(std::max(0l, pages)) * groups_[g].page_size);
         }
         return best;
+    }
+
+    // What `admit` did for a request.
+    struct Admission {
+        bool ok = false;
+        size_t cached_pages = 0;     // leading pages found in the cache and taken over
+        uint64_t chain = 0;          // hash of the last of them (0: none)
+    };
+
+    // Admission as one transaction: the request `seq` with `n` known tokens gets, or does not get,
+    // everything it needs to start: the cached pages of its prefix (never the page that holds its
+    // last token: that token's logits are wanted, so it has to be computed), room for all `n` tokens
+    // in the groups that keep every token (reserved now, so that a later admission cannot take it;
+    // window groups are reserved portion by portion) with `watermark` pages to spare in every group,
+    // and a state slot.  When anything is missing nothing has changed.
+    Admission admit(SeqId seq, const int32_t* tokens, size_t n, size_t portion_tokens, bool use_prefix) {
+        Admission out;
+        if (n == 0 || tables_.count(seq) || slot_of_.count(seq)) throw std::logic_error("admit: request is empty or holds something already");
+        std::vector<uint64_t> names;
+        if (use_prefix && prefix_reuse_possible()) names = page_hashes(tokens, n - 1, groups_[0].page_size);
+        std::vector<int> kept;
+        const size_t found = prefix_match(names, &kept);
+        if (!fits(n, portion_tokens, found, kept) || free_slots_.empty()) return out;
+        if (found > 0) {
+            adopt_prefix(seq, names, found);
+            out.chain = names[found - 1];
+        }
+        acquire_state_slot(seq);
+        if (!reserve(seq, n, /*windows_too=*/false)) throw std::logic_error("admit: room was checked");
+        out.ok = true;
+        out.cached_pages = found;
+        return out;
     }
 
     // Starts `seq` on the cached pages of the first n hashes (all full pages).

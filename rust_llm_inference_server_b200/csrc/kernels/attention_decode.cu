@@ -691,7 +691,9 @@ __global__ __launch_bounds__(DEC_THREADS) void attn_decode_mma_kernel(
     }
 }
 
-// Ticket counters of the fused merge, part of the library image, zero between launches.
+// Ticket counters of the fused merge, part of the library image, zero between launches.  One array
+// for every launch of the process that merges by tickets: launches that overlap on the GPU (different
+// streams, no dependency between them) would share cells, so callers order them.
 constexpr int kMaxTickets = 65536;
 __device__ int g_decode_tickets[kMaxTickets];
 

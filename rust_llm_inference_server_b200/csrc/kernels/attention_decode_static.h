@@ -25,6 +25,15 @@
 //    to start at zero: each (request, head, split) cell that the merge reads is written by this
 //    call's first kernel.  Two calls that overlap on the GPU (different streams, no dependency)
 //    race on the array: order them.
+//  * The same holds between this entry point and the ordinary ones.  Where the splits are merged by
+//    "the last ticket folds", every decode-attention launch of the process, whichever entry point
+//    made it, counts its tickets in one array of the library image, indexed by (request, kv head).
+//    Two such launches that overlap on the GPU would count into each other's cells, and a merge
+//    could run early or not at all.  Launches on one stream are ordered by the stream; launches on
+//    different streams have to be ordered by the caller (an event), whatever their scratch buffers.
+//  * The two look-ups of device addresses (this array's and the ticket array's) are kept in plain
+//    per-device variables.  Two host threads that make the first call on a device at the same time
+//    both do the look-up and store the same value; nothing else is shared between host threads.
 #pragma once
 
 #include <cuda_runtime.h>

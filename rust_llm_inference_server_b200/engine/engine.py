@@ -145,7 +145,8 @@ class LLMEngine:
             for g in groups:
                 g.num_pages = int(cfg.num_blocks)
         else:
-            size_groups(groups, cfg.kv_cache_bytes, elem)
+            size_groups(groups, cfg.kv_cache_bytes, elem, cfg.max_num_seqs,
+                        max(cfg.max_batched_tokens, cfg.max_num_seqs))
         if any(g.num_pages < 2 for g in groups):
             raise ValueError(f"kv cache of {cfg.kv_cache_bytes} bytes holds fewer than 2 blocks")
         self.groups = groups

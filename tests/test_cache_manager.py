@@ -86,6 +86,43 @@ def test_groups_reserve_together_or_not_at_all():
     assert m.check_invariants() == ""
 
 
+def test_admission_is_one_transaction_over_pages_prefix_and_state_slots():
+    """A request gets the cached pages of its prefix, room for all its tokens in the groups that
+    keep everything, and a state slot, or nothing at all."""
+    m = mgr(groups=[H.GroupConfig(8, 4, 0), H.GroupConfig(6, 4, 8)], slots=2)
+    m.set_watermark(1)
+    toks = list(range(20))
+    assert m.admit(1, toks, 8) == (True, 0)              # (no prefix reuse with a window group)
+    assert m.reserved_tokens(1, 0) == 20 and m.table(1, 1) == [] and m.state_slot(1) >= 0
+    # the keep-all group has 3 pages left: 12 tokens and the watermark do not fit
+    snapshot = (m.num_free_pages(0), m.num_free_pages(1), m.num_free_state_slots())
+    assert m.admit(2, list(range(12)), 8) == (False, 0)
+    assert (m.num_free_pages(0), m.num_free_pages(1), m.num_free_state_slots()) == snapshot and not m.contains(2)
+    assert m.admit(2, list(range(8)), 8) == (True, 0)
+    # no state slot left: nothing changes either
+    snapshot = (m.num_free_pages(0), m.num_free_pages(1))
+    assert m.admit(3, [1], 8) == (False, 0) and (m.num_free_pages(0), m.num_free_pages(1)) == snapshot
+    with pytest.raises(RuntimeError):
+        m.admit(1, toks, 8)                              # holds something already
+    m.free(1); m.free(2)
+    assert m.check_invariants() == ""
+    # a window group is asked for its window plus one portion, not for the whole request
+    w = mgr(groups=[H.GroupConfig(64, 4, 0), H.GroupConfig(5, 4, 8)], slots=2)
+    w.set_watermark(0)
+    assert w.admit(1, list(range(100)), 8) == (True, 0)      # 8 + 8 tokens: 4 of 5 pages
+    assert w.admit(2, list(range(100)), 16) == (False, 0)    # 8 + 16 tokens: 6 pages
+    # prefix reuse: the pages of a finished request are taken over, except the one with the last token
+    p = mgr(pages=8, ps=4, slots=2)
+    p.set_watermark(0)
+    assert p.admit(1, toks, 8) == (True, 0)
+    for i, h in enumerate(H.page_hashes(toks, 4)):
+        p.register_page(1, i, h)
+    p.free(1)
+    assert p.admit(2, toks, 8) == (True, 4) and p.reserved_tokens(2, 0) == 20    # 5 full pages, 4 taken over
+    assert p.admit(3, toks[:9] + [77, 78], 8, False) == (True, 0)                # asked not to look
+    assert p.check_invariants() == ""
+
+
 def test_state_slots_are_unique_and_return():
     m = mgr(slots=2)
     a, b = m.acquire_state_slot(1), m.acquire_state_slot(2)
@@ -152,3 +189,18 @@ def test_random_operations_keep_every_invariant(seed):
         for g in range(m.num_groups()):    # the full pool returns
             assert m.num_free_pages(g) == m.group(g).num_pages
         assert m.num_free_state_slots() == 5
+
+
+def test_pool_sizing_caps_window_groups_at_what_they_can_hold():
+    from rust_llm_inference_server_b200.cache import plan_groups, size_groups
+    from rust_llm_inference_server_b200.parts import KVCacheSpec
+    specs = [KVCacheSpec(2, 64, None), KVCacheSpec(2, 64, 128), KVCacheSpec(2, 64, None)]
+    groups = plan_groups(specs, 16)
+    assert [g.slots for g in groups] == [[0, 2], [1]] and [g.window for g in groups] == [0, 128]
+    size_groups(groups, 1 << 26, 2)
+    assert groups[0].num_pages == groups[1].num_pages            # no seats known: equal shares
+    equal = groups[0].num_pages
+    size_groups(groups, 1 << 26, 2, max_num_seqs=4, max_batched_tokens=256)
+    assert groups[1].num_pages == 4 * ((128 + 256) // 16 + 2) and groups[0].num_pages > equal
+    used = sum(g.num_pages * g.bytes_per_page(2) for g in groups)
+    assert used <= 1 << 26 and (1 << 26) - used < sum(g.bytes_per_page(2) for g in groups)
