@@ -20,6 +20,16 @@
 // through global memory, and no CTA waits for another one at the end.  The number of splits depends on N and K only, never on the rows, so a token's
 // result does not depend on its neighbours.
 //
+// With more than 16 rows that exchange is slow: every counted store is an update of the finisher's
+// one mbarrier, and a tile of 64 rows spent 5 of its 13 us sending (timestamps in the kernel).
+// Tiles of 32 and 64 rows are summed by features instead: the 128 features of a tile are 16 chunks
+// of 8, chunk c is finished by CTA c % splits, and a thread sends the sums of its feature for 16
+// tokens as four plain 16-byte stores into a [sender][4 tokens][feature][token] area of the
+// finisher (the 8 lanes of a chunk write 128 contiguous bytes); a second cluster barrier makes them
+// visible, and the finisher's threads add the senders in split order for (feature, token) pairs and
+// store 8 features of a token side by side.  The order of the additions is the same as before, so
+// the result is too.
+//
 // The first stages of W are requested before the kernel waits for its predecessor in the stream
 // (programmatic dependent launch): weights are written by nobody, so the stream of weights goes
 // on across the kernel boundary, and only x and y wait.
@@ -35,8 +45,9 @@
 // Sending a row of partial sums as one bulk copy from a staging area in shared memory, counted once
 // on the finisher's mbarrier, instead of 128 counted stores, with the cluster barrier at the end
 // that the staging area then needs: 5.6 -> 6.6 us for the QKV product of 8 rows, the step 0.87 ->
-// 0.93 ms.  With 17 to 32 rows a layer's four products take 46 us, with 64 rows 64 us, against 39 us
-// for the library (plus its gating and norm kernels), so longer batches go to the library GEMM.)
+// 0.93 ms.  With 17 to 32 rows a layer's four products take 39 us, with 64 rows 51 us (46 and 64 us
+// while those tiles were summed token by token), against 39 us for the library (plus its gating
+// kernel), so batches of more than 32 rows go to the library GEMM.)
 //
 // Epilogues: bf16 or float32 y, or SwiGLU on a gate|up matrix whose rows are interleaved in blocks
 // of 4 (rows 8t..8t+3 gate, 8t+4..8t+7 up): y[m, 4t + j] = silu(gate_j) * up_j.
@@ -111,6 +122,19 @@ __device__ __forceinline__ void st_async_f32(float* local, float v, uint64_t* ba
                  ::"r"(raddr), "r"(__float_as_uint(v)), "r"(rbar) : "memory");
 }
 
+// Four floats into the shared memory of the cluster's CTA `rank` (16-byte aligned), a plain store:
+// a cluster barrier orders it before the reads.
+__device__ __forceinline__ void st_cluster_f32x4(float* local, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t rank) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Tiles of 32 and 64 rows are summed by chunks of 8 features (see the head of the file).
+template <int NT> __host__ __device__ constexpr bool by_features() { return NT == 32 || NT == 64; }
+constexpr int CHUNK_F = 8;                   // features of a chunk
+constexpr int N_CHUNKS = SF / CHUNK_F;       // 16 chunks a tile
+
 template <int EPI, typename OutT>
 __device__ __forceinline__ void store_token(OutT* __restrict__ y, float v, int t, int f, int lane, int N) {
     if (EPI == 1) {
@@ -153,8 +177,11 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     constexpr uint32_t IDESC = idesc_bf16(SF, NT);
     unsigned char* w_tiles = base;
     constexpr int STG = stages_of<NT>();
-    static_assert((size_t)(NT + MAX_SPLITS - 1) * SF * 4 <= (size_t)STG * (W_STAGE_BYTES + NT * SK * 2),
+    static_assert(by_features<NT>() || (size_t)(NT + MAX_SPLITS - 1) * SF * 4 <= (size_t)STG * (W_STAGE_BYTES + NT * SK * 2),
                   "the stages must hold the rows of partial sums that the cluster sends");
+    // by features: up to N_CHUNKS + splits - 1 (chunk, sender) blocks of 8 features x NT floats
+    static_assert(!by_features<NT>() || (size_t)(N_CHUNKS + MAX_SPLITS - 1) * CHUNK_F * NT * 4 <= (size_t)STG * (W_STAGE_BYTES + NT * SK * 2),
+                  "the stages must hold the blocks of partial sums that the cluster sends");
     unsigned char* x_tiles = base + (size_t)STG * W_STAGE_BYTES;
     SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)STG * X_STAGE_BYTES);
 
@@ -178,7 +205,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         // tokens split, split + splits, ... are finished by this CTA: every CTA of the cluster
         // sends a row of 128 floats for each of them
         const int owned = split < M ? (M - split + splits - 1) / splits : 0;
-        if (splits > 1 && owned > 0) bar_expect_tx(&ctrl->red_full, (uint32_t)(owned * splits * SF * 4));
+        if (!by_features<NT>() && splits > 1 && owned > 0) bar_expect_tx(&ctrl->red_full, (uint32_t)(owned * splits * SF * 4));
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     }
@@ -281,6 +308,51 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         // reads anybody's shared memory, so nobody has to be waited for at the end.
         float* part = reinterpret_cast<float*>(w_tiles);
         cluster_sync_all();
+        if constexpr (by_features<NT>()) {
+            // this thread's feature belongs to chunk ch, which CTA ch % splits finishes; there it is block
+            // (ch / splits) * splits + split, laid out [group of 4 tokens][feature of 8][token of 4]
+            const int ch = (int)threadIdx.x / CHUNK_F, fi = (int)threadIdx.x % CHUNK_F;
+            float* dst = part + ((ch / splits) * splits + split) * (CHUNK_F * NT) + fi * 4;
+            const uint32_t to = (uint32_t)(ch % splits);
+#pragma unroll 1
+            for (int c = 0; c < NT / 16; ++c) {
+                if (c * 16 >= M) break;
+                uint32_t r[16];
+                if (has_work) {
+                    tmem_ld16(tmem_acc + (uint32_t)(c * 16), r);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                    st_cluster_f32x4(dst + ((c * 16 + j) / 4) * (CHUNK_F * 4), r[j], r[j + 1], r[j + 2], r[j + 3], to);
+            }
+            cluster_sync_all();                 // what was sent has arrived; nobody touches another CTA's memory from here on
+            // thread -> feature fi of the chunk and tokens tg, tg + 16, ...: the 8 features of a token are
+            // neighbouring lanes (the SwiGLU pairs four lanes apart, 16-byte runs of y)
+            const int tg = (int)threadIdx.x / CHUNK_F;
+#pragma unroll 1
+            for (int c2 = split, slot = 0; c2 < N_CHUNKS; c2 += splits, ++slot) {
+                const int fo = n0 + c2 * CHUNK_F + fi;
+#pragma unroll 1
+                for (int t = tg; t < ((M + 15) & ~15); t += S_THREADS / CHUNK_F) {
+                    const float* src = part + (slot * splits) * (CHUNK_F * NT) + (t / 4) * (CHUNK_F * 4) + fi * 4 + (t & 3);
+                    float v = 0.f;
+                    for (int sdr = 0; sdr < splits; ++sdr) v += src[sdr * (CHUNK_F * NT)];
+                    const float sc = scaled && t < M ? ctrl->rstd[t] : 1.0f;
+                    if (EPI == 1) {
+                        // (every lane takes part in the exchange of the gated epilogue; rows past M are not stored)
+                        const float g = v * sc;
+                        const float other = __shfl_xor_sync(0xffffffffu, g, 4);
+                        if (ok && t < M && (fi & 4) == 0 && fo + 4 < N)
+                            y[(size_t)t * (N >> 1) + ((fo >> 3) << 2) + (fo & 3)] = from_f<OutT>(g / (1.0f + expf(-g)) * other);
+                    } else if (ok && t < M && fo < N) {
+                        y[(size_t)t * N + fo] = from_f<OutT>(v * sc);
+                    }
+                }
+            }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < NT / 16; ++c) {
             if (c * 16 >= M) break;
@@ -313,6 +385,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                     store_token<EPI, OutT>(y, v * (scaled ? ctrl->rstd[t] : 1.0f), t, f, lane, N);
                 }
             }
+        }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -164,7 +164,11 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 
 FUSE_NORMS = True          # debug switch "fuse_norms": 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
-DECODE_GEMM_ROWS = 16     # up to this many rows `linear` uses it; longer batches go to the library GEMM
+DECODE_GEMM_ROWS = 16     # up to this many rows its sink epilogue works: the norms go into the products
+STREAM_GEMM_ROWS = 32     # up to this many rows `linear` uses it; longer batches go to the library GEMM
+                          # (debug switch "stream_rows"; measured in the decode step at the 1B sizes, context
+                          # 4096: 24 and 32 requests 1.381 and 1.540 ms with it, 1.390 and 1.541 ms with the
+                          # library; 48 and 64 requests 1.976 and 2.369 ms against 1.894 and 2.226 ms)
 
 
 class ScaledRows:
@@ -290,7 +294,7 @@ def fuses_norms(n_rows: int, dtype, *widths: int) -> bool:
 
 def linear(x, w: torch.Tensor, out_dtype=None, sink: ResidualSink | None = None):
     """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
-    16 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
+    32 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
     accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits).
     ScaledRows as x and a `sink` are for the streaming kernel only (see `fuses_norms`)."""
     if isinstance(x, ScaledRows) or sink is not None:
@@ -303,7 +307,7 @@ def linear(x, w: torch.Tensor, out_dtype=None, sink: ResidualSink | None = None)
         raise KernelError(f"linear: expected matching float32 or bfloat16 operands, got {x.dtype}, {w.dtype}")
     if not x.is_cuda:
         raise KernelError("linear: expected CUDA tensors; there is no CPU path")
-    if x.shape[0] <= DECODE_GEMM_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
+    if x.shape[0] <= STREAM_GEMM_ROWS and x.shape[1] % 8 == 0 and x.is_contiguous():
         return stream_gemm(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
@@ -506,7 +510,13 @@ def _set_flag(name):
     return setter
 
 
-library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"))
+def _set_stream_rows(value):
+    global STREAM_GEMM_ROWS
+    STREAM_GEMM_ROWS = max(DECODE_GEMM_ROWS, min(int(value), STREAM_MAX_ROWS))
+
+
+library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
+                               stream_rows=_set_stream_rows)
 
 
 def attention_prefill(q, k_cache, v_cache, out, tiles, cu_seqlens, ctx_lens, block_tables,

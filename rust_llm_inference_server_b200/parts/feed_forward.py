@@ -44,7 +44,7 @@ class SwiGLU(FeedForward):
     def forward(self, x, step, sink=None):
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
         with span("mlp gate+up, silu*up"):
-            if fusable and x.shape[0] <= ops.DECODE_GEMM_ROWS:
+            if fusable and x.shape[0] <= ops.STREAM_GEMM_ROWS:
                 act = ops.stream_gemm(x, self.w_gate_up, swiglu4=True)       # product and gating in one kernel
             elif fusable and x.shape[0] >= 128 and self.spec.intermediate % 128 == 0:
                 # prefill: the tcgen05 product with the gating in its epilogue (the gate|up activations

@@ -88,7 +88,8 @@ def test_float32_matrix_product_is_true_float32_and_row_independent(shape):
 
 @pytest.mark.parametrize("shape", [(1, 8, 8), (8, 3072, 2048), (3, 301, 80), (16, 520, 176), (13, 64, 8200), (5, 1000, 96),
                                    (8, 20000, 2048), (2, 2048, 8192), (4, 1500, 4104), (17, 520, 264), (40, 3072, 2048),
-                                   (100, 1096, 1032), (128, 2048, 8192)])
+                                   (100, 1096, 1032), (128, 2048, 8192), (24, 3072, 2048), (32, 301, 80), (64, 2048, 8192),
+                                   (48, 16384, 2048), (33, 1000, 4104), (64, 136, 64), (20, 128, 2048)])
 def test_streaming_product_for_decode_rows(shape):
     """The tcgen05 weight-streaming kernel: few and many features (one CTA, clusters of 2 to 16
     splitting k), k that is no multiple of a stage, every row count up to 128."""
@@ -102,7 +103,7 @@ def test_streaming_product_for_decode_rows(shape):
     got16 = ops.stream_gemm(dev(x), dev(w)).cpu()
     assert bool(((got16.double() - want).abs() <= 2.0 ** -8 * want.abs() + 1e-4).all())
     assert torch.equal(ops.stream_gemm(dev(x), dev(w)).cpu(), got16)                  # the same again: no race in the sums
-    if M <= ops.DECODE_GEMM_ROWS:
+    if M <= ops.STREAM_GEMM_ROWS:
         assert torch.equal(ops.linear(dev(x), dev(w)).cpu(), got16)               # `linear` takes this path
     one = ops.stream_gemm(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w), torch.float32).cpu()
     assert torch.equal(one[0], got32[M // 2])                                     # a row ignores its neighbours
@@ -168,7 +169,8 @@ def test_streaming_product_refuses_what_it_cannot_take():
         ops.stream_gemm(dev(torch.randn(2, 36).bfloat16()), dev(torch.randn(8, 36).bfloat16()))
 
 
-@pytest.mark.parametrize("I,K,M", [(8, 16, 2), (176, 80, 7), (8192, 2048, 8), (500, 264, 33), (1024, 512, 128)])
+@pytest.mark.parametrize("I,K,M", [(8, 16, 2), (176, 80, 7), (8192, 2048, 8), (500, 264, 33), (1024, 512, 128),
+                                   (8192, 2048, 24), (448, 320, 64), (388, 2048, 32)])
 def test_streaming_product_with_gating_and_interleaved_gating_kernel(I, K, M):
     from rust_llm_inference_server_b200 import ops
     torch.manual_seed(I)
