@@ -47,7 +47,8 @@
 // that the staging area then needs: 5.6 -> 6.6 us for the QKV product of 8 rows, the step 0.87 ->
 // 0.93 ms.  With 17 to 32 rows a layer's four products take 39 us, with 64 rows 51 us (46 and 64 us
 // while those tiles were summed token by token), against 39 us for the library (plus its gating
-// kernel), so batches of more than 32 rows go to the library GEMM.)
+// kernel), and in the step the library is as fast at 32 rows and faster with larger matrices, so
+// batches of more than 16 rows go to the library GEMM.)
 //
 // Epilogues: bf16 or float32 y, or SwiGLU on a gate|up matrix whose rows are interleaved in blocks
 // of 4 (rows 8t..8t+3 gate, 8t+4..8t+7 up): y[m, 4t + j] = silu(gate_j) * up_j.

@@ -165,10 +165,11 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
 FUSE_NORMS = True          # debug switch "fuse_norms": 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
 DECODE_GEMM_ROWS = 16     # up to this many rows its sink epilogue works: the norms go into the products
-STREAM_GEMM_ROWS = 32     # up to this many rows `linear` uses it; longer batches go to the library GEMM
-                          # (debug switch "stream_rows"; measured in the decode step at the 1B sizes, context
-                          # 4096: 24 and 32 requests 1.381 and 1.540 ms with it, 1.390 and 1.541 ms with the
-                          # library; 48 and 64 requests 1.976 and 2.369 ms against 1.894 and 2.226 ms)
+STREAM_GEMM_ROWS = 16     # up to this many rows `linear` uses it; longer batches go to the library GEMM
+                          # (debug switch "stream_rows"; measured in the decode step with 32 rows: at the 1B
+                          # sizes, context 4096, 1.540 ms with it and 1.541 ms with the library; at the 8B
+                          # sizes, two layers, context 8192, 0.863 against 0.770 ms; with 48 and 64 rows at
+                          # the 1B sizes 1.976 and 2.369 ms against 1.894 and 2.226 ms)
 
 
 class ScaledRows:
@@ -294,7 +295,7 @@ def fuses_norms(n_rows: int, dtype, *widths: int) -> bool:
 
 def linear(x, w: torch.Tensor, out_dtype=None, sink: ResidualSink | None = None):
     """y = x @ w^T for w stored (out, in).  float32: this package's FFMA kernel.  bfloat16: up to
-    32 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
+    16 rows go to this package's weight-streaming tcgen05 kernel, more to the library GEMM; both
     accumulate in float32, and `out_dtype=torch.float32` keeps that precision (used for logits).
     ScaledRows as x and a `sink` are for the streaming kernel only (see `fuses_norms`)."""
     if isinstance(x, ScaledRows) or sink is not None:

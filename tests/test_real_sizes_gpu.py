@@ -113,9 +113,8 @@ def test_llama_1b_layer_sizes_against_the_plain_implementation(model_root, dtype
 def test_many_requests_prefilled_in_one_step_and_decoded_together(model_root, which, n_req, lo, hi, dtype):
     """The reference's paged batch (crates/model/tests/parity.rs:254-324): all prompts in one
     step, then 32 steps in which every request decodes one token, over block tables whose pages
-    are interleaved among the requests.  In bfloat16 a step of more than 16 rows runs the norms as
-    kernels, the streaming product without its norm epilogues (up to 32 rows) or the library
-    product (40 rows here), and decode attention with few pieces: the batch-64 point of the
+    are interleaved among the requests.  In bfloat16 a step of more than 16 rows takes the library
+    product, the norm kernels and decode attention with few pieces: the batch-64 point of the
     benchmark runs this path and no other test does."""
     from rust_llm_inference_server_b200 import ops
     cfg = CONFIGS[which]
