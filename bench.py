@@ -419,6 +419,25 @@ def workload_1b_fp32(args, torch, np) -> dict:
     }
 
 
+def print_timeline(records: list) -> None:
+    """One decode step product by product (microseconds since the first product of the step started):
+    when the launch's first CTA started, when its wait for the kernel before it passed, when its
+    products were done, and when it ended; the gap is from the end of the product before to this
+    one's wait passing, which for QKV -> O holds the attention kernel."""
+    if not records:
+        return
+    t0 = records[0]["start"]
+    us = lambda v: "      -" if v is None else f"{(v - t0) / 1e3:7.2f}"
+    print(f"{'N x K':>15} | {'start':>7} {'waited':>7} {'done':>7} {'barrier':>7} {'sent':>7} {'arrived':>7} {'end':>7} | after the wait | gap before",
+          file=sys.stderr)
+    prev = None
+    for r in records:
+        gap = "" if prev is None else f"{(r['wait_passed'] - prev) / 1e3:6.2f}"
+        print(f"{r['N']:>7} x {r['K']:>5} | {us(r['start'])} {us(r['wait_passed'])} {us(r['products_done'])} {us(r['cluster_barrier'])} "
+              f"{us(r['sent'])} {us(r['sums_arrived'])} {us(r['end'])} | {(r['end'] - r['wait_passed']) / 1e3:14.2f} | {gap:>10}", file=sys.stderr)
+        prev = r["end"]
+
+
 WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32}
 
 
@@ -441,6 +460,10 @@ def main() -> int:
                     help="one of the other measured configurations instead of the default line: 3b (continuous "
                          "batching under a Poisson stream), 8b (batch 32 at 8,192 of context), 1b-fp32")
     ap.add_argument("--rate", type=float, default=48.0, help="--workload 3b: mean arrivals a second")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --only decode and RLIS_TIMELINE=1 in the environment (a build of the kernels with "
+                         "the stamps compiled in): lay the last step out product by product from the stamps the "
+                         "streaming products' first CTAs take of the device's timer (printed to stderr)")
     ap.add_argument("--spans", action="store_true",
                     help="with --only: time the stages of the step with CUDA-event spans (RLIS_PROFILE) and "
                          "print the table to stderr; steps then run eagerly, not from graphs")
@@ -455,7 +478,7 @@ def main() -> int:
     import numpy as np
     import torch
 
-    from rust_llm_inference_server_b200 import LLM, SamplingParams
+    from rust_llm_inference_server_b200 import LLM, SamplingParams, ops
     from rust_llm_inference_server_b200.ops import profile
 
     if args.workload:
@@ -487,9 +510,13 @@ def main() -> int:
     if args.only and args.spans:
         profile.enable(True)
     if args.only == "decode":
+        if args.timeline:
+            ops.stream_timeline(True)
         ms, launches = decode_run(llm, B, args.steps, args.warmup, context, torch, fill=not args.no_fill)
         print(json.dumps({"only": "decode", "batch": B, "context": context, "ms_per_step": round(ms, 4),
                           "launches_per_step": launches}))
+        if args.timeline:
+            print_timeline(ops.read_stream_timeline(4 * n_layers + 1))
         if args.spans:
             print(profile.format_report(profile.take_report()), file=sys.stderr)
         return 0

@@ -90,6 +90,24 @@ template <int NT> constexpr size_t stream_smem_bytes() {
     return (size_t)stages_of<NT>() * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
 }
 
+// A timeline for measurements, compiled in only with -DRLIS_TIMELINE (the build adds it when the
+// environment has RLIS_TIMELINE=1; even switched off it cost the decode step 1 %): the first CTA of
+// every launch stamps the global timer at its phases into a ring of records, which the host reads
+// after a step.  With it a step replayed from a graph can be laid out product by product without a
+// tracing tool.
+//   0 start, 1 the wait for the kernel before has passed, 2 the products are done, 3 the cluster's
+//   barrier, 4 the partial sums are sent, 5 the sums for this CTA's tokens have arrived, 7 end;
+//   6 holds N * 100000 + K.
+constexpr int TL_RECORDS = 512;
+#ifdef RLIS_TIMELINE
+__device__ int g_timeline_on;
+__device__ unsigned int g_timeline_n;
+__device__ unsigned long long g_timeline[TL_RECORDS][8];
+#define TL_STAMP(i) do { if (tl_on) g_timeline[tl_slot][i] = now_ns(); } while (0)
+#else
+#define TL_STAMP(i) do { } while (0)
+#endif
+
 struct SCtrl {
     uint64_t full[S_STAGES];
     uint64_t empty[S_STAGES];
@@ -186,6 +204,15 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     unsigned char* x_tiles = base + (size_t)STG * W_STAGE_BYTES;
     SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)STG * X_STAGE_BYTES);
 
+#ifdef RLIS_TIMELINE
+    const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && g_timeline_on != 0;
+    unsigned tl_slot = 0;
+    if (tl_on) {
+        tl_slot = atomicAdd(&g_timeline_n, 1u) % (unsigned)TL_RECORDS;
+        g_timeline[tl_slot][6] = (unsigned long long)N * 100000ull + (unsigned long long)K;
+    }
+#endif
+    TL_STAMP(0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
     const int n0 = tile * SF;
@@ -257,6 +284,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     }
     __syncwarp();
     pdl_wait();            // nothing is stored before the kernels before this one have finished
+    TL_STAMP(1);
     const bool scaled = EPI != 2 && nf.in_partials != nullptr;
     if (scaled && (int)threadIdx.x < M) {
         // this token's scale: the partial sums in the order of the tiles (RMSNorm: 1 / sqrt(mean + eps))
@@ -274,6 +302,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     }
     const bool waited = has_work ? bar_wait(&ctrl->acc_full, 0, &ctrl->abort) : true;
     const bool ok = __syncthreads_and(waited ? 1 : 0) != 0;       // the same for all threads
+    TL_STAMP(2);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // epilogue: warp w reads TMEM lanes 32 w .. 32 w + 31; lane = feature, column = token
@@ -309,6 +338,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         // reads anybody's shared memory, so nobody has to be waited for at the end.
         float* part = reinterpret_cast<float*>(w_tiles);
         cluster_sync_all();
+        TL_STAMP(3);
         if constexpr (by_features<NT>()) {
             // this thread's feature belongs to chunk ch, which CTA ch % splits finishes; there it is block
             // (ch / splits) * splits + split, laid out [group of 4 tokens][feature of 8][token of 4]
@@ -372,8 +402,10 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                                  &ctrl->red_full, (uint32_t)(t % splits));
             }
         }
+        TL_STAMP(4);
         if (split < M) {
             const bool got = bar_wait(&ctrl->red_full, 0, &ctrl->abort);
+            TL_STAMP(5);
             const bool good = EPI == 2 ? __syncthreads_and(ok && got ? 1 : 0) != 0 : (ok && got);
 #pragma unroll 1
             for (int t = split, slot = 0; t < M; t += splits, ++slot) {
@@ -389,6 +421,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         }
         }
     }
+    TL_STAMP(7);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 2) {
@@ -443,6 +476,31 @@ int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, 
 }
 }  // namespace
 
+// The timeline of the launches (see g_timeline): switch, and read-out of the ring [512][8] with the
+// number of records written so far.  Both synchronise the device.
+// Both synchronise the device; RLIS_ERR_UNSUPPORTED from a library built without the timeline.
+extern "C" int rlis_stream_gemm_timeline(int on) {
+#ifdef RLIS_TIMELINE
+    const unsigned int zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_timeline_n, &zero, sizeof(zero));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_timeline_on, &on, sizeof(on));
+    return (int)e;
+#else
+    (void)on;
+    return RLIS_ERR_UNSUPPORTED;
+#endif
+}
+extern "C" int rlis_stream_gemm_timeline_read(unsigned long long* out, unsigned int* n) {
+#ifdef RLIS_TIMELINE
+    cudaError_t e = cudaMemcpyFromSymbol(n, g_timeline_n, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * TL_RECORDS * 8);
+    return (int)e;
+#else
+    (void)out;
+    (void)n;
+    return RLIS_ERR_UNSUPPORTED;
+#endif
+}
 extern "C" int rlis_stream_gemm_error(void) { return tc::read_error_word(); }
 extern "C" int* rlis_stream_gemm_error_addr(void) { return tc::error_word_addr(); }
 

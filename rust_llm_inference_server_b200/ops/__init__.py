@@ -277,6 +277,36 @@ def take_device_errors(out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def stream_timeline(on: bool) -> None:
+    """Switches the streaming products' timeline on or off (and empties it): the first CTA of every
+    launch stamps the device's global timer at its phases.  A measurement tool; synchronises.  Only in
+    a library built with it: set RLIS_TIMELINE=1 in the environment before the first use."""
+    torch.cuda.synchronize()
+    check(lib().rlis_stream_gemm_timeline(1 if on else 0), "stream_timeline")
+
+
+def read_stream_timeline(last: int) -> list:
+    """The last `last` launches of the streaming product (oldest first), each a dict with N, K and,
+    in nanoseconds of the global timer: start, wait_passed (the kernel before has finished),
+    products_done, cluster_barrier, sent, sums_arrived (the last three None for a launch that does
+    not split k) and end."""
+    import ctypes
+    torch.cuda.synchronize()
+    buf = (ctypes.c_ulonglong * (512 * 8))()
+    n = ctypes.c_uint(0)
+    check(lib().rlis_stream_gemm_timeline_read(buf, ctypes.byref(n)), "stream_timeline_read")
+    count = min(int(last), n.value, 512)
+    out = []
+    for i in range(n.value - count, n.value):
+        r = buf[(i % 512) * 8:(i % 512) * 8 + 8]
+        split = r[3] >= r[2] and r[3] <= r[7]          # records of launches without a split keep stale stamps there
+        out.append({"N": int(r[6] // 100000), "K": int(r[6] % 100000), "start": int(r[0]), "wait_passed": int(r[1]),
+                    "products_done": int(r[2]), "cluster_barrier": int(r[3]) if split else None,
+                    "sent": int(r[4]) if split else None, "sums_arrived": int(r[5]) if split else None,
+                    "end": int(r[7])})
+    return out
+
+
 def check_device_errors() -> None:
     """Raises if a bounded wait inside a kernel ever ran out on this device (the kernel then
     finished without its data; results since are not to be trusted).  Synchronises the device."""

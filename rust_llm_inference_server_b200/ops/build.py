@@ -133,12 +133,18 @@ def build_kernels() -> str:
     if not srcs:
         raise BuildError(f"no kernel sources under {CSRC}/kernels")
 
+    # RLIS_TIMELINE=1: a second library with the streaming products' timeline compiled in (a
+    # measurement build; see stream_gemm_tcgen05.cu), beside the ordinary one
+    timeline = os.environ.get("RLIS_TIMELINE", "0") not in ("", "0")
+    flags = NVCC_FLAGS + (["-DRLIS_TIMELINE"] if timeline else [])
+
     def cmd(out):
         if out == "OUT":
-            return NVCC_FLAGS
-        return [_find_nvcc()] + NVCC_FLAGS + ["-o", out] + srcs
+            return flags
+        return [_find_nvcc()] + flags + ["-o", out] + srcs
 
-    return _ensure("librlis_kernels.so", srcs, hdrs, cmd, "CUDA kernels (sm_100a)")
+    name = "librlis_kernels_timeline.so" if timeline else "librlis_kernels.so"
+    return _ensure(name, srcs, hdrs, cmd, "CUDA kernels (sm_100a)" + (" with the timeline" if timeline else ""))
 
 
 def build_host() -> str:

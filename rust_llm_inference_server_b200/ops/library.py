@@ -43,6 +43,8 @@ SIGNATURES = {
     "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
     "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, P],
     "rlis_take_errors": [P, P],
+    "rlis_stream_gemm_timeline": [I],
+    "rlis_stream_gemm_timeline_read": [P, P],
     "rlis_attention_decode_last_variant": [],
 }
 
