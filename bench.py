@@ -428,13 +428,14 @@ def print_timeline(records: list) -> None:
         return
     t0 = records[0]["start"]
     us = lambda v: "      -" if v is None else f"{(v - t0) / 1e3:7.2f}"
-    print(f"{'N x K':>15} | {'start':>7} {'waited':>7} {'done':>7} {'barrier':>7} {'sent':>7} {'arrived':>7} {'end':>7} | after the wait | gap before",
+    print(f"{'N x K':>15} | {'start':>7} {'waited':>7} {'done':>7} {'barrier':>7} {'sent':>7} {'arrived':>7} {'end':>7} | after the wait | gap before | grid before done",
           file=sys.stderr)
     prev = None
     for r in records:
         gap = "" if prev is None else f"{(r['wait_passed'] - prev) / 1e3:6.2f}"
         print(f"{r['N']:>7} x {r['K']:>5} | {us(r['start'])} {us(r['wait_passed'])} {us(r['products_done'])} {us(r['cluster_barrier'])} "
-              f"{us(r['sent'])} {us(r['sums_arrived'])} {us(r['end'])} | {(r['end'] - r['wait_passed']) / 1e3:14.2f} | {gap:>10}", file=sys.stderr)
+              f"{us(r['sent'])} {us(r['sums_arrived'])} {us(r['end'])} | {(r['end'] - r['wait_passed']) / 1e3:14.2f} | {gap:>10} | {us(r['grid_before_done'])}",
+              file=sys.stderr)
         prev = r["end"]
 
 

@@ -97,12 +97,14 @@ template <int NT> constexpr size_t stream_smem_bytes() {
 // tracing tool.
 //   0 start, 1 the wait for the kernel before has passed, 2 the products are done, 3 the cluster's
 //   barrier, 4 the partial sums are sent, 5 the sums for this CTA's tokens have arrived, 7 end;
-//   6 holds N * 100000 + K.
+//   6 holds N * 100000 + K; 8 the latest end of any CTA of the streaming product launched before
+//   (read after the wait: when that whole grid was done, not only its first CTA).
 constexpr int TL_RECORDS = 512;
 #ifdef RLIS_TIMELINE
 __device__ int g_timeline_on;
 __device__ unsigned int g_timeline_n;
-__device__ unsigned long long g_timeline[TL_RECORDS][8];
+__device__ unsigned long long g_timeline[TL_RECORDS][10];
+__device__ unsigned long long g_timeline_last_end;
 #define TL_STAMP(i) do { if (tl_on) g_timeline[tl_slot][i] = now_ns(); } while (0)
 #else
 #define TL_STAMP(i) do { } while (0)
@@ -285,6 +287,9 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     __syncwarp();
     pdl_wait();            // nothing is stored before the kernels before this one have finished
     TL_STAMP(1);
+#ifdef RLIS_TIMELINE
+    if (tl_on) g_timeline[tl_slot][8] = *reinterpret_cast<volatile unsigned long long*>(&g_timeline_last_end);
+#endif
     const bool scaled = EPI != 2 && nf.in_partials != nullptr;
     if (scaled && (int)threadIdx.x < M) {
         // this token's scale: the partial sums in the order of the tiles (RMSNorm: 1 / sqrt(mean + eps))
@@ -422,6 +427,9 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
         }
     }
     TL_STAMP(7);
+#ifdef RLIS_TIMELINE
+    if (threadIdx.x == 64 && g_timeline_on != 0) atomicMax(&g_timeline_last_end, now_ns());
+#endif
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 2) {
@@ -476,7 +484,7 @@ int dispatch_stream(const void* x, const void* W, void* y, int M, int N, int K, 
 }
 }  // namespace
 
-// The timeline of the launches (see g_timeline): switch, and read-out of the ring [512][8] with the
+// The timeline of the launches (see g_timeline): switch, and read-out of the ring [512][10] with the
 // number of records written so far.  Both synchronise the device.
 // Both synchronise the device; RLIS_ERR_UNSUPPORTED from a library built without the timeline.
 extern "C" int rlis_stream_gemm_timeline(int on) {
@@ -493,7 +501,7 @@ extern "C" int rlis_stream_gemm_timeline(int on) {
 extern "C" int rlis_stream_gemm_timeline_read(unsigned long long* out, unsigned int* n) {
 #ifdef RLIS_TIMELINE
     cudaError_t e = cudaMemcpyFromSymbol(n, g_timeline_n, sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * TL_RECORDS * 8);
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_timeline, sizeof(unsigned long long) * TL_RECORDS * 10);
     return (int)e;
 #else
     (void)out;

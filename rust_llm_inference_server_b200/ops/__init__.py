@@ -289,21 +289,22 @@ def read_stream_timeline(last: int) -> list:
     """The last `last` launches of the streaming product (oldest first), each a dict with N, K and,
     in nanoseconds of the global timer: start, wait_passed (the kernel before has finished),
     products_done, cluster_barrier, sent, sums_arrived (the last three None for a launch that does
-    not split k) and end."""
+    not split k), end, and grid_before_done: the latest end of any CTA of the streaming product launched
+    before this one (meaningful when that product is the kernel right before)."""
     import ctypes
     torch.cuda.synchronize()
-    buf = (ctypes.c_ulonglong * (512 * 8))()
+    buf = (ctypes.c_ulonglong * (512 * 10))()
     n = ctypes.c_uint(0)
     check(lib().rlis_stream_gemm_timeline_read(buf, ctypes.byref(n)), "stream_timeline_read")
     count = min(int(last), n.value, 512)
     out = []
     for i in range(n.value - count, n.value):
-        r = buf[(i % 512) * 8:(i % 512) * 8 + 8]
+        r = buf[(i % 512) * 10:(i % 512) * 10 + 10]
         split = r[3] >= r[2] and r[3] <= r[7]          # records of launches without a split keep stale stamps there
         out.append({"N": int(r[6] // 100000), "K": int(r[6] % 100000), "start": int(r[0]), "wait_passed": int(r[1]),
                     "products_done": int(r[2]), "cluster_barrier": int(r[3]) if split else None,
                     "sent": int(r[4]) if split else None, "sums_arrived": int(r[5]) if split else None,
-                    "end": int(r[7])})
+                    "end": int(r[7]), "grid_before_done": int(r[8])})
     return out
 
 
