@@ -50,12 +50,15 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
         const int key = kb + lane;
         const bool valid = key >= lo && key <= pos;
         float s = -INFINITY;
+        // where this lane's key and value rows start (elements), or -1: hidden, or a page the host did not map
+        long long row_off = -1;
         if (valid) {
             const int page = table[key / page_size];
             if (page < 0) {
                 s = NAN;  // a page the host did not map: make it visible, never read outside
             } else {
-                const T* krow = k_cache + (((size_t)page * nkv + kvh) * page_size + key % page_size) * d;
+                row_off = (((long long)page * nkv + kvh) * page_size + key % page_size) * d;
+                const T* krow = k_cache + row_off;
                 float dot = 0.f;
                 for (int j = 0; j < d; j += VN) {
                     float kv[VN];
@@ -72,18 +75,22 @@ __global__ __launch_bounds__(WARPS * 32) void attn_generic_kernel(
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        // p . v in the order of the keys.  The rows' addresses come from the lanes that own the keys,
+        // not from the table again, and a key without weight takes part with a zero that is selected,
+        // not multiplied (its row may hold anything): no load waits for a branch, so the loads of
+        // several keys are in flight together.
+#pragma unroll 8
         for (int kk = 0; kk < 32; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, p, kk);
-            if (pk != 0.f) {  // uniform over the warp
-                const int kidx = kb + kk;
-                const int page = table[kidx / page_size];
-                if (page >= 0) {
-                    const T* vrow = v_cache + (((size_t)page * nkv + kvh) * page_size + kidx % page_size) * d;
+            const long long off = __shfl_sync(0xffffffffu, row_off, kk);
+            const bool use = pk != 0.f && off >= 0;  // uniform over the warp
+            const T* vrow = v_cache + (use ? off : 0);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int dim = lane + 32 * i;
-                        if (dim < d) acc[i] = fmaf(pk, to_f<T>(vrow[dim]), acc[i]);
-                    }
+            for (int i = 0; i < 8; ++i) {
+                const int dim = lane + 32 * i;
+                if (dim < d) {
+                    const float v = to_f<T>(vrow[dim]);
+                    acc[i] = use ? fmaf(pk, v, acc[i]) : acc[i];
                 }
             }
         }
