@@ -17,12 +17,14 @@ extern "C" int rlis_get_pdl(void) { return g_rlis_pdl; }
 // can hold one choice fixed.  Nothing in the engine sets them.
 //   pdl              0 / 1     programmatic dependent launch
 //   stream_ctas      n         about how many CTAs a weight-streaming product is cut into (0: automatic)
+//   stream_min_stages n        stages of the ring a product's CTA is given at least (0: what its k uses; -1: automatic)
 //   decode_stages    0, 2..4   stages of keys in flight in decode attention (0: automatic)
 //   decode_cluster   0 / 1     merge decode attention's pieces inside a cluster where possible
 //   decode_tma       0 / 1     fetch decode attention's keys by bulk tensor copies where possible
 //   prefill_splits   0,1,2,4   CTAs that share a tile's keys in the tcgen05 prefill attention (0: automatic)
 //   filtered_cluster 0 / 1     the cluster kernel of top-k / top-p sampling where the vocabulary fits
 extern "C" void rlis_stream_gemm_set_target(int);
+extern "C" void rlis_stream_gemm_set_min_stages(int);
 extern "C" void rlis_attention_decode_set_stages(int);
 extern "C" void rlis_attention_decode_set_cluster(int);
 extern "C" void rlis_attention_decode_set_tma(int);
@@ -33,6 +35,7 @@ extern "C" int rlis_debug_set(const char* name, int value) {
     if (name == nullptr) return RLIS_ERR_UNSUPPORTED;
     if (!strcmp(name, "pdl")) rlis_set_pdl(value);
     else if (!strcmp(name, "stream_ctas")) rlis_stream_gemm_set_target(value);
+    else if (!strcmp(name, "stream_min_stages")) rlis_stream_gemm_set_min_stages(value);
     else if (!strcmp(name, "decode_stages")) rlis_attention_decode_set_stages(value);
     else if (!strcmp(name, "decode_cluster")) rlis_attention_decode_set_cluster(value);
     else if (!strcmp(name, "decode_tma")) rlis_attention_decode_set_tma(value);

@@ -86,8 +86,8 @@ constexpr int W_STAGE_BYTES = SF * SK * 2;
 constexpr int S_THREADS = 128;
 constexpr int MAX_SPLITS = 16;          // the largest cluster (above 8 is opt-in)
 
-template <int NT> constexpr size_t stream_smem_bytes() {
-    return (size_t)stages_of<NT>() * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
+template <int NT> constexpr size_t stream_smem_bytes(int n_stages = stages_of<NT>()) {
+    return (size_t)n_stages * (W_STAGE_BYTES + NT * SK * 2) + 1024 /* alignment */ + 768 /* SCtrl */;
 }
 
 // A timeline for measurements, compiled in only with -DRLIS_TIMELINE (the build adds it when the
@@ -190,7 +190,7 @@ template <int NT, int EPI, typename OutT>
 __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 OutT* __restrict__ y, int M, int N, int K,
-                                                                int kb_per_split, const NormFuse nf) {
+                                                                int kb_per_split, int n_stages, const NormFuse nf) {
     extern __shared__ unsigned char sg_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sg_smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int X_STAGE_BYTES = NT * SK * 2;
@@ -203,8 +203,12 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
     // by features: up to N_CHUNKS + splits - 1 (chunk, sender) blocks of 8 features x NT floats
     static_assert(!by_features<NT>() || (size_t)(N_CHUNKS + MAX_SPLITS - 1) * CHUNK_F * NT * 4 <= (size_t)STG * (W_STAGE_BYTES + NT * SK * 2),
                   "the stages must hold the blocks of partial sums that the cluster sends");
-    unsigned char* x_tiles = base + (size_t)STG * W_STAGE_BYTES;
-    SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)STG * X_STAGE_BYTES);
+    // A CTA with fewer blocks of k than the ring has stages never wraps around and is given only the
+    // stages it uses (n_stages, the same for the whole launch): a product with little k per CTA then
+    // takes half the shared memory and fits beside the kernels before and after it, whose CTAs it
+    // would otherwise have to wait for before it can request its weights.
+    unsigned char* x_tiles = base + (size_t)n_stages * W_STAGE_BYTES;
+    SCtrl* ctrl = reinterpret_cast<SCtrl*>(x_tiles + (size_t)n_stages * X_STAGE_BYTES);
 
 #ifdef RLIS_TIMELINE
     const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && g_timeline_on != 0;
@@ -439,6 +443,7 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
 }
 
 int g_target_ctas = 0;      // 0: twice the number of SMs
+int g_min_stages = -1;      // stages a CTA is given at least (measurements; -1: by the rows, see launch_stream)
 
 template <int NT, int EPI, typename OutT>
 int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, const NormFuse& nf, cudaStream_t stream) {
@@ -468,9 +473,25 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, co
     if (splits < 1) splits = 1;
     const int per = (k_blocks + splits - 1) / splits;
     splits = (k_blocks + per - 1) / per;
+    // stages: what a CTA's blocks of k use, and what the cluster's exchange of partial sums needs
+    constexpr int STG = stages_of<NT>();
+    const size_t stage_bytes = (size_t)W_STAGE_BYTES + (size_t)NT * SK * 2;
+    size_t exchange = 0;
+    if (splits > 1)
+        exchange = by_features<NT>() ? (size_t)((N_CHUNKS + splits - 1) / splits) * splits * CHUNK_F * NT * 4
+                                     : (size_t)((M + splits - 1) / splits) * splits * SF * 4;
+    // (Measured in the decode step of a 1B Llama, context 4096.  One request: every product with the
+    // stages it uses 0.706 ms, with three at least 0.716, with all four 0.718: the products that fit
+    // beside their neighbours request their weights earlier.  Eight requests: 0.883, 0.876 and
+    // 0.884 ms: there the kernel before the O projection streams keys and values, and two-stage CTAs
+    // of the projection, all resident at once, compete with it.)
+    int min_stages = g_min_stages >= 0 ? g_min_stages : (M <= 2 ? 0 : 3);
+    int n_stages = per < STG ? per : STG;
+    if (n_stages < min_stages) n_stages = min_stages < STG ? min_stages : STG;
+    while (n_stages < STG && (size_t)n_stages * stage_bytes < exchange) ++n_stages;
     rlis_launch_cluster(stream_gemm_kernel<NT, EPI, OutT>, dim3((unsigned)tiles, (unsigned)splits), S_THREADS,
-                        stream_smem_bytes<NT>(), stream, dim3(1, (unsigned)splits, 1), map_w, map_x, (OutT*)y, M, N, K,
-                        per, nf);
+                        stream_smem_bytes<NT>(n_stages), stream, dim3(1, (unsigned)splits, 1), map_w, map_x, (OutT*)y, M, N, K,
+                        per, n_stages, nf);
     return RLIS_LAUNCH_CHECK();
 }
 
@@ -514,6 +535,7 @@ extern "C" int* rlis_stream_gemm_error_addr(void) { return tc::error_word_addr()
 
 // About how many CTAs a launch is cut into (0: twice the SMs).  For measurements.
 extern "C" void rlis_stream_gemm_set_target(int ctas) { g_target_ctas = ctas; }
+extern "C" void rlis_stream_gemm_set_min_stages(int n) { g_min_stages = n; }
 
 // out_dtype: RLIS_BF16 or RLIS_F32.  epilogue 0: y [M, N]; 1 (SwiGLU, rows of W interleaved
 // gate/up in blocks of 4, N a multiple of 8): y [M, N / 2].  M up to 128; K a multiple of 8;
