@@ -46,6 +46,13 @@
 // (a 256-token portion at 8192 tokens of context: 114 -> 54 us; with enough tiles to fill the SMs
 // the sharing only costs, so it is used when the CTAs fit the SMs at once).
 //
+// (A whole prompt of 2048 tokens is 512 CTAs for 296 places, and its last tiles are chains of 16
+// blocks where a place gets 15 on average.  Sharing only the tiles with more than 11 blocks between
+// two CTAs was measured both ways and lost both times: as clusters of two whose second CTA leaves at
+// once for a short tile, 56 -> 84 us (a grid of clusters that oversubscribes the SMs schedules
+// badly), and as two ordinary CTAs that leave their rows in a scratch buffer for the one that takes
+// the tile's last ticket, 57 -> 78 us; at 4096 tokens and more nothing is shared and nothing changes.)
+//
 // Every mbarrier wait is bounded (a fifth of a second); a wait that runs out sets the error word
 // (rlis_attention_prefill_tc_error), every role runs to its end without further waits, and the
 // CTA frees its tensor memory before it returns.
