@@ -1,6 +1,6 @@
-"""Each part of a layer alone, built from its spec and a dictionary of tensors, against the plain
-function of the same part: norm, position encoding, attention mixer (with and without a window,
-with and without rotation), feed-forward, and the pre-norm block."""
+"""Each part alone, built from its spec and a dictionary of tensors, against the plain function of
+the same part: embedding, norm, position encoding, attention mixer (with and without a window,
+with and without rotation), feed-forward, the pre-norm block, and the LM head."""
 
 import math
 
@@ -15,11 +15,16 @@ pytestmark = pytest.mark.gpu
 
 class DictSource:
     def __init__(self, tensors, dtype):
-        self.t, self.dtype = tensors, dtype
+        self.t, self.dtype, self.shared = tensors, dtype, {}
 
-    def get(self, name, role="matrix"):
+    def get(self, name, role="matrix", share=False):
+        if share and (name, role) in self.shared:
+            return self.shared[(name, role)]
         x = self.t[name].cuda()
-        return x.to(self.dtype) if role == "matrix" else x.float()
+        x = x.to(self.dtype) if role == "matrix" else x.float()
+        if share:
+            self.shared[(name, role)] = x
+        return x
 
 
 class FakeStep:
@@ -209,3 +214,38 @@ def test_prenorm_block(dtype):
     got = resid.cpu() + delta.float().cpu()
     want = P.decoder_layer(x, w, 1, TINY_C, torch.arange(T))
     assert (got - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_lm_head_parts(dtype):
+    """The two ends of the residual stream as parts: the table's rows widened to float32 (times a
+    scale when the spec gives one), and float32 logits of chosen rows (scaled and capped smoothly
+    when the spec says so); a tied pair shares one tensor on the device."""
+    from rust_llm_inference_server_b200.parts import EmbeddingSpec, LMHeadSpec, build_embedding, build_lm_head
+    V, H, T = 301, 80, 23
+    g = torch.Generator().manual_seed(5)
+    tensors = {"emb": (torch.randn(V, H, generator=g) * 0.5).bfloat16().float(),
+               "head": (torch.randn(V, H, generator=g) * 0.5).bfloat16().float()}
+    src = DictSource(tensors, dtype)
+    ids = torch.randint(0, V, (T,), generator=g)
+    step = FakeStep([0], [T], 8, [list(range(4))])
+    for scale in (None, 3.5):
+        emb = build_embedding(EmbeddingSpec(V, H, "emb", scale=scale), dtype, "cuda")
+        assert emb.tensors() == {"emb": (V, H)}
+        emb.load(src)
+        out = torch.empty(T, H, dtype=torch.float32, device="cuda")
+        emb.forward(ids.to(torch.int32).cuda(), out, step)
+        want = P.embedding(ids, tensors["emb"]) * (1.0 if scale is None else np.float32(scale))
+        assert torch.equal(out.cpu(), want)                   # a row select and one float32 product: exact
+    h = (torch.randn(T, H, generator=g)).to(dtype)
+    for name, ls, cap in (("emb", None, None), ("head", 2.0, None), ("head", None, 3.0), ("emb", 0.5, 1.25)):
+        head = build_lm_head(LMHeadSpec(V, H, name, logit_scale=ls, soft_cap=cap), dtype, "cuda")
+        head.load(src)
+        if name == "emb":
+            assert head.weight is emb.weight                  # tied: one copy
+        got = head.forward(h.cuda(), step)
+        assert got.dtype == torch.float32 and got.shape == (T, V)
+        want = P.linear(h.float(), tensors[name]) * (1.0 if ls is None else ls)
+        if cap is not None:
+            want = cap * torch.tanh(want / cap)
+        assert (got.cpu() - want).abs().max() <= (2e-5 if dtype == torch.float32 else 2e-2) * max(1.0, float(want.abs().max()))
