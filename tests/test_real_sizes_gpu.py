@@ -18,9 +18,16 @@ pytestmark = pytest.mark.gpu
 TOPK = 64
 BOUND = {"float32": 5e-4, "bfloat16": 0.15}
 NEAR_TIE = 0.02
+# With random weights the rounding errors at two candidates are independent, and top-2 margins of a
+# few hundredths are common, so the margin rule above needs the size of the noise beside it.  The
+# noise is measured on every row (the rms error over the whole vocabulary: 0.0094 of the logits'
+# spread at the 1B sizes, 0.0112 at the 3B sizes in bfloat16, 3e-6 and 4e-6 in float32, the same for whole prompts, single tokens and
+# mixed steps) and bounded; a choice may then differ where the margin is below four times that
+# row's own noise.  A fault at a row raises its noise past the bound long before it reaches 0.15.
+ROW_NOISE = {"float32": 1e-5, "bfloat16": 0.015}      # rms error of a row / spread of its logits
 
 
-def check_rows(got: np.ndarray, ref: np.ndarray, dtype: str, what: str):
+def check_rows(got: np.ndarray, ref: np.ndarray, dtype: str, what: str, noise_rule: bool = False):
     assert got.shape == ref.shape and np.isfinite(got).all(), what
     worst = 0.0
     for r in range(ref.shape[0]):
@@ -29,9 +36,15 @@ def check_rows(got: np.ndarray, ref: np.ndarray, dtype: str, what: str):
         lse_g = float(torch.logsumexp(torch.from_numpy(got[r]), 0))
         lse_r = float(torch.logsumexp(torch.from_numpy(ref[r]), 0))
         worst = max(worst, d, abs(lse_g - lse_r))
+        near = NEAR_TIE
+        if noise_rule:
+            noise = float(np.sqrt(np.mean((got[r].astype(np.float64) - ref[r]) ** 2)))
+            assert noise <= ROW_NOISE[dtype] * float(ref[r].std()), \
+                f"{what}: row {r} has rms error {noise} over logits of spread {ref[r].std()}"
+            near = max(near, 4 * noise)
         a, b = int(np.argmax(got[r])), int(top[0])
         if a != b:
-            assert dtype != "float32" and ref[r, b] - ref[r, a] < NEAR_TIE, \
+            assert dtype != "float32" and ref[r, b] - ref[r, a] < near, \
                 f"{what}: row {r} picks {a}, the plain implementation {b} by {ref[r, b] - ref[r, a]}"
     assert worst <= BOUND[dtype], f"{what}: top-{TOPK} logits / logsumexp differ by {worst}"
     return worst
@@ -43,12 +56,13 @@ def session(model_root, which, dtype, max_tokens, page_size=16):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_llama_1b_layer_sizes_against_the_plain_implementation(model_root, dtype):
-    """H 2048, 32 query : 8 key/value heads of 64, I 8192, V 128256, llama3 scaling, tied; seed 4.
+@pytest.mark.parametrize("which", ["1B2L", "3B2L"])
+def test_llama_layer_sizes_against_the_plain_implementation(model_root, which, dtype):
+    """Two layers at the sizes of Llama 3.2 1B (H 2048, 32 query : 8 key/value heads of 64, I 8192,
+    seed 4) and 3B (H 3072, 24 : 8 heads of 128, seed 5); V 128256, llama3 scaling, tied.
     A prompt whole; most of it in one step and the last 32 tokens one by one; and steps that mix a
     portion of one request with single tokens of another."""
     from rust_llm_inference_server_b200 import ops
-    which = "1B2L"
     cfg = CONFIGS[which]
     rng = np.random.default_rng(21)
     a = rng.integers(0, cfg["vocab_size"], size=301).tolist()
@@ -64,14 +78,14 @@ def test_llama_1b_layer_sizes_against_the_plain_implementation(model_root, dtype
 
     # whole
     out = s.step({"step": 0, "entries": [{"id": "a", "tokens": a, "want": rows_a}], "end": ["a"]})
-    check_rows(out.numpy(), ref_a, dtype, f"1B sizes {dtype} whole")
+    check_rows(out.numpy(), ref_a, dtype, f"{which} {dtype} whole", noise_rule=True)
     # most of it in one step, the last 32 one by one
     head = 301 - 32
     got = [s.step({"step": 1, "entries": [{"id": "a", "tokens": a[:head], "want": [head - 1]}], "end": []}).numpy()]
     for i in range(head, 301):
         got.append(s.step({"step": 2 + i, "entries": [{"id": "a", "tokens": [a[i]], "want": [0]}],
                            "end": ["a"] if i == 300 else []}).numpy())
-    check_rows(np.concatenate(got), ref_a[-33:], dtype, f"1B sizes {dtype} last 32 one by one")
+    check_rows(np.concatenate(got), ref_a[-33:], dtype, f"{which} {dtype} last 32 one by one", noise_rule=True)
     # mixed: b's first 100 tokens, then b token by token beside portions of a
     s.step({"step": 400, "entries": [{"id": "b", "tokens": b[:100], "want": []}], "end": []})
     got_b, pos_a, k = [], 0, 0
@@ -96,14 +110,15 @@ def test_llama_1b_layer_sizes_against_the_plain_implementation(model_root, dtype
         if len(entries) == 2:
             pos_a += n
     assert pos_a == 301
-    check_rows(np.stack(got_b), ref_b, dtype, f"1B sizes {dtype} single tokens beside portions")
-    check_rows(np.stack([got_a[r] for r in rows_a]), ref_a, dtype, f"1B sizes {dtype} portions beside single tokens")
+    check_rows(np.stack(got_b), ref_b, dtype, f"{which} {dtype} single tokens beside portions", noise_rule=True)
+    check_rows(np.stack([got_a[r] for r in rows_a]), ref_a, dtype, f"{which} {dtype} portions beside single tokens", noise_rule=True)
     s.step({"step": 999, "entries": [], "end": ["a", "b"]})
     assert s.cache.check_invariants() == "" and s.cache.num_free_pages(0) == s.cache.group(0).num_pages
     if dtype == "bfloat16":
         for k in ("attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma",
                   "gemm_tcgen05.swiglu4", "stream_gemm.sink", "stream_gemm.scaled.swiglu"):
             assert ops.launches_by_kernel.get(k), (k, sorted(ops.launches_by_kernel))
+        assert not ops.launches_by_kernel.get("attention_prefill.mma") and not ops.launches_by_kernel.get("attention_generic")
         assert s.runner._graph_launches > 0
     ops.check_device_errors()
 

@@ -71,8 +71,19 @@ ONE_B_2L = {
     "max_position_embeddings": 131072, "tie_word_embeddings": True,
 }
 
-SEEDS = {"A": 0, "B": 2, "C": 7, "D": 11, "E": 13, "1B2L": 4}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "1B2L": ONE_B_2L}
+# The layer sizes of Llama 3.2 3B with two layers: heads of 128 in groups of three.
+THREE_B_2L = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 3072, "intermediate_size": 8192, "num_hidden_layers": 2,
+    "num_attention_heads": 24, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072, "tie_word_embeddings": True,
+}
+
+SEEDS = {"A": 0, "B": 2, "C": 7, "D": 11, "E": 13, "1B2L": 4, "3B2L": 5}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "1B2L": ONE_B_2L, "3B2L": THREE_B_2L}
 
 
 def make_model_dir(tmp_root: str, which: str, store_dtype: str = "bfloat16") -> str:
