@@ -9,23 +9,45 @@
 // instruction are (head 0, tokens 0..63), (head 1, tokens 0..63), so every key and value tile is
 // used by both heads (a group of three heads is a pair and a head that is taken twice, its copy's
 // rows dropped).  Per block of 128 keys:
-//   warp 0, one lane: TMA.  Q once (two 64 x 64 boxes); the block's K and V page by page (a page
-//           of one kv head is a [page_size x 64] box of the cache seen as a 2-D tensor; pages
-//           past the context are asked for past the end of the tensor and arrive as zeros) into
-//           rings of two tiles for the keys and two for the values, 128-byte swizzle.  A key tile
-//           is free once its scores are done, a block earlier than its value tile: with one ring
-//           for both, the keys of the next block were asked for so late that the products waited
-//           for them (1.8 us a block and CTA, most of it that wait).
-//   warp 1, one lane: S = Q K^T (tcgen05.mma, M 128, N 128, K 64) into tensor memory; after the
-//           softmax warps have written P: O += P V (M 128, N 64, K 128; V is the MN-major
-//           operand, straight from the cache's layout), accumulated in tensor memory.
-//   warps 2-5: a thread per row.  It takes its row of S out of tensor memory at once, finds the
-//           maximum, writes P = exp2(s - reference) rounded to bf16 into shared memory in the
-//           swizzled K-major layout the tensor core reads.  The reference follows the maximum
-//           only when that has run ahead by more than 2^8; then, rarely after the first blocks,
-//           the warp rescales its rows of O in tensor memory before the next product.
-// Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
-// other's gaps between the phases.
+//   warp 0: TMA.  Q once (two 64 x 64 boxes); the block's K and V page by page (a page of one kv
+//           head is a [page_size x 64] box of the cache seen as a 2-D tensor; pages past the
+//           context are asked for past the end of the tensor and arrive as zeros), a page a lane,
+//           into rings of three tiles for the keys and three for the values, 128-byte swizzle.  A
+//           key tile is free once its scores are done, a block earlier than its value tile.
+//   warp 1: S = Q K^T (tcgen05.mma, M 128, N 128, K 64) into tensor memory; then O += P V (M 128,
+//           N 64, K 128; P is the A operand read from tensor memory, V the MN-major B operand,
+//           straight from the cache's layout), accumulated in tensor memory, in two bursts: the
+//           first half of the keys as soon as the softmax warps have written that half of P.
+//   warps 4-7: a thread per row.  It takes its row of S out of tensor memory at once, finds the
+//           maximum, writes P = exp2(s - reference) rounded to bf16 back into tensor memory, two
+//           keys to a column.  The reference follows the maximum only when that has run ahead by
+//           more than 2^8; then, rarely after the first blocks, the warp rescales its rows of O
+//           in tensor memory before the next product.
+// Two CTAs fit an SM (112 KB of shared memory, 256 columns of tensor memory each: S 128, O 64,
+// P 64) and fill each other's gaps between the phases.  The CTA starts with 128 registers a
+// thread; warps 0-3 (two of them idle) give theirs up to 40 and the softmax warps take 216.
+//
+// What the cycle stamps of an instrumented build showed, and what followed from them (8192 tokens,
+// a block of one CTA with two on the SM, before: 3660 cycles):
+//   * A burst of tensor instructions costs its issuing thread about 300 cycles before the first is
+//     through and 50 each after that, whatever their size (a micro-benchmark of M 128, N 64 ... 256
+//     says the same), and the products are done almost as soon as the last is issued.  The eight of
+//     P V were 900 cycles between the last exponential and the next block's first; in two bursts
+//     the second is 500.
+//   * With P in a swizzled tile of shared memory the CTA moved 144 KB a block through shared memory
+//     (the products' operands, P written and read, the arriving tiles); with P in tensor memory 80.
+//   * The special-function unit does four exponentials a cycle and scheduler: 1024 cycles for a
+//     warp's 32 rows of 128 keys.  A lone warp reaches one every 12 cycles, two warps of a
+//     scheduler together one every 8.4: the two CTAs of an SM are in their exponentials at the
+//     same time most of the time (1900 cycles) and the unit idles in between (a third of the time).
+//     More registers for the softmax warps, a three-input maximum in four chains (520 -> 300
+//     cycles) and two float32 to an instruction for the scaling and the sums are small change
+//     beside that.
+//   Now: a block 3040 cycles; 8192 tokens 535 -> 469 us (586 TFLOP/s), 2048 tokens 59 -> 48 us.
+//   (Measured and dropped: four heads a CTA with two softmax groups over one ring of tiles and one
+//   issuing thread, 627 us at 8192, the thread's bursts one after the other being the bound; the
+//   same with the two groups taking turns at the exponentials, 672 us; handing the halves of P
+//   back one by one after their own bursts instead of waiting for the whole product, 485 us.)
 //
 // Head size 128 is the same kernel with blocks of 64 keys, so that the tiles are as large and two
 // CTAs still fit: a row of Q, K or V is two 128-byte lines, kept as two swizzled sub-tiles of 64
@@ -37,9 +59,10 @@
 // against 56.9 us at 2048 tokens, 623 against 535 us at 8192: a block's chain of handshakes does
 // not shrink with the block.)
 //
-// (Measured at 8192 tokens, 32:8 heads, pages of 16: 706 us, 389 TFLOP/s; the mma.sync kernel
-// 1356 us.  One lane issuing a block's sixteen page copies: 972 us whatever the softmax warps did.
-// Eight softmax warps, two threads a row with a softmax stream and an accumulator each: 822 us.)
+// (Earlier measurements at 8192 tokens, 32:8 heads, pages of 16: the mma.sync kernel 1356 us.  One
+// lane issuing a block's sixteen page copies: 972 us whatever the softmax warps did.  Eight softmax
+// warps, two threads a row with a softmax stream and an accumulator each, P in shared memory: 822
+// against 706 us.)
 //
 // A short portion of a long prompt is few tiles with many blocks each: 2 or 4 CTAs of a cluster then
 // take a tile's blocks in turn and rank 0 merges their rows through distributed shared memory
@@ -64,28 +87,34 @@ using namespace tc;
 constexpr int TQ = 64;                  // tokens of a CTA
 static_assert(TQ == RLIS_PREFILL_TILE, "the host's tile list is cut for another tile size");
 constexpr int TM = 128;                 // rows of the instruction: two heads x 64 tokens
-constexpr int KV_STAGES = 2;
-constexpr int PT_THREADS = 192;
+constexpr int MAX_KV_STAGES = 3;
+constexpr int PT_THREADS = 256;         // warps 0-3: copies, products and two idle ones; warps 4-7: softmax
+constexpr int PT_SOFTMAX_WARP0 = 4;
 constexpr int LINE_TILE = TM * 128;     // bytes of a swizzled sub-tile of 128 rows: 64 columns, 128-byte lines
-constexpr uint32_t TMEM_COLS = 256;     // S: columns 0 .. TN - 1, O: 128 .. 128 + HD - 1
+constexpr uint32_t TMEM_COLS = 256;     // S: columns 0 .. TN - 1, O: 128 .. 128 + HD - 1, P (bf16 pairs): TN / 2 columns in what is left
 
-// Sizes by head size HD and keys of a block TN (64, 128) or (128, 64): 112 KB of tiles either way.
+// Sizes by head size HD and keys of a block TN (64, 128) or (128, 64): 16 KB of keys and of values a
+// block, three blocks in flight for head size 64 and two for 128 (112 and 96 KB a CTA, two CTAs an SM).
 template <int HD, int TN> struct PShape {
     static constexpr int Q_BYTES = TM * HD * 2;             // 16 or 32 KB: HD / 64 sub-tiles [128 x 64]
     static constexpr int KV_TILE_BYTES = TN * HD * 2;       // 16 KB each for K and V: HD / 64 sub-tiles [TN x 64]
     static constexpr int KV_LINE_TILE = TN * 128;           // bytes of one such sub-tile
-    static constexpr int P_BYTES = TM * TN * 2;             // 32 or 16 KB: TN / 64 sub-tiles [128 x 64]
+    static constexpr int KV_STAGES = HD == 64 ? 3 : 2;
     // the tiles + the control block; with the kilobyte the system keeps per CTA, two CTAs fit the
     // 228 KB of an SM only if no alignment slack is spent: the dynamic array is declared 1024-aligned
-    static constexpr size_t SMEM = Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES + 128;
+    static constexpr size_t SMEM = Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 256;
     static constexpr uint32_t IDESC_S = idesc_bf16(TM, TN);
     static constexpr uint32_t IDESC_PV = idesc_bf16(TM, HD) | (1u << 16);      // B (V) is MN-major
+    static constexpr uint32_t P_COL = HD == 64 ? 192u : 64u;   // where P lives in tensor memory
     static constexpr int ROW_F = HD + 4;                    // floats a row in the clusters' exchange area
     static constexpr int MAX_SPLITS = HD == 64 ? 4 : 2;     // what that area holds: (splits - 1) * 128 rows
-    static_assert((MAX_SPLITS - 1) * TM * ROW_F * 4 <= Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + P_BYTES,
+    static_assert((MAX_SPLITS - 1) * TM * ROW_F * 4 <= Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES,
                   "the exchange area of the cluster merge does not fit the tiles");
-    static_assert(TN == 64 || TN == 128, "a block of keys is one or two swizzled sub-tiles of P");
-    static_assert(TN + 0 <= 128 && HD <= 128, "S and O share 256 columns of tensor memory");
+    static_assert(TN == 64 || TN == 128, "a block of keys");
+    static_assert(KV_STAGES <= MAX_KV_STAGES, "the control block's barriers");
+    static_assert(TN <= 128 && HD <= 128 && (HD == 64 ? TN / 2 <= 64 : TN + TN / 2 <= 128),
+                  "S, P and O share 256 columns of tensor memory");
+    static_assert(2 * (SMEM + 1024) <= 228 * 1024, "two CTAs an SM");
 };
 
 // Shared-memory descriptor of the MN-major operand V under the 128-byte swizzle: lines of 64 head
@@ -98,9 +127,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(const void* tile, uint32_
 
 struct PCtrl {
     uint64_t q_full;
-    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];     // keys and values have rings of their own: a key
-    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];     // tile is free a whole block before its value tile
-    uint64_t s_full, s_empty, p_full, o_full;
+    uint64_t k_full[MAX_KV_STAGES], k_empty[MAX_KV_STAGES];     // keys and values have rings of their own: a key
+    uint64_t v_full[MAX_KV_STAGES], v_empty[MAX_KV_STAGES];     // tile is free a whole block before its value tile
+    uint64_t s_full, s_empty, p_full[2], o_full;    // P arrives in two halves of the block's keys
     uint32_t tmem_base;
     int abort;
 };
@@ -121,17 +150,53 @@ __device__ __forceinline__ void max_of_chunk(const uint32_t (&v)[32], int c, int
     }
 }
 
-// P = exp2(s * scale - m) of 32 keys, rounded to bf16 into the row's line of the swizzled tile (two
-// halves of 64 keys; the 16-byte chunk index is XORed with the row's index in its group of 8).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void max_of_chunk3(const uint32_t (&v)[32], float& mx) {
+    float m[4] = {mx, -INFINITY, -INFINITY, -INFINITY};      // four chains: one would be 16 dependent instructions
+#pragma unroll
+    for (int i = 0; i < 32; i += 8)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[j] = max3(m[j], __uint_as_float(v[i + 2 * j]), __uint_as_float(v[i + 2 * j + 1]));
+    mx = max3(m[0], m[1], fmaxf(m[2], m[3]));
+}
+
+// Two float32 to an instruction (the softmax warps are bound by the instructions they issue as
+// much as by the special-function unit): d = a * b + c and acc += a on pairs.
+__device__ __forceinline__ uint64_t pair_of(float x) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, uint64_t b, uint64_t c) {
+    asm("{\n.reg .b64 ra, rd;\nmov.b64 ra, {%2, %3};\nfma.rn.f32x2 rd, ra, %4, %5;\nmov.b64 {%0, %1}, rd;\n}\n"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "l"(b), "l"(c));
+}
+__device__ __forceinline__ void add2(uint64_t& acc, uint32_t a0, uint32_t a1) {
+    asm("{\n.reg .b64 ra;\nmov.b64 ra, {%1, %2};\nadd.rn.f32x2 %0, %0, ra;\n}\n" : "+l"(acc) : "r"(a0), "r"(a1));
+}
+__device__ __forceinline__ float sum_of_pair(uint64_t acc) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc));
+    return lo + hi;
+}
+
+// P = exp2(s * scale - m) of 32 keys, rounded to bf16, into the row's lane of tensor memory: two
+// consecutive keys to a column, the layout in which the tensor core reads its A operand from there.
+// `lsum2`: the running sums of the even and of the odd keys.
 template <bool MASK>
-__device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int kmin, int kmax, float scale_log2,
-                                             float m_use, unsigned char* prow, int r, float& lsum) {
+__device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int kmin, int kmax, uint64_t scale2,
+                                             uint64_t neg_m2, uint32_t tmem_p_row, uint64_t& lsum2) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int idx = c * 32 + 2 * i;
-        float p0 = ex2_approx(fmaf(__uint_as_float(v[2 * i]), scale_log2, -m_use));
-        float p1 = ex2_approx(fmaf(__uint_as_float(v[2 * i + 1]), scale_log2, -m_use));
+        float x0, x1;
+        fma2(x0, x1, __uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), scale2, neg_m2);
+        float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
         if (MASK) {
             if (!(idx <= kmax && idx >= kmin)) p0 = 0.f;
             if (!(idx + 1 <= kmax && idx + 1 >= kmin)) p1 = 0.f;
@@ -139,16 +204,10 @@ __device__ __forceinline__ void exp_of_chunk(const uint32_t (&v)[32], int c, int
         // the sum is of the rounded values, the ones the product with V uses: the rounding of a
         // dominant key then cancels between numerator and denominator
         const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-        lsum += __low2float(h) + __high2float(h);
         pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+        add2(lsum2, pk[i] << 16, pk[i] & 0xffff0000u);
     }
-    unsigned char* half = prow + (size_t)(c / 2) * LINE_TILE;
-#pragma unroll
-    for (int ch = 0; ch < 4; ++ch) {
-        const int chunk = (c % 2) * 4 + ch;
-        *reinterpret_cast<uint4*>(half + (((chunk ^ (r & 7)) & 7) << 4)) =
-            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-    }
+    tmem_st16(tmem_p_row + (uint32_t)(c * 16), pk);
 }
 
 // 32 float32 sums of a row, times `inv`, as bf16 to `dst` (16-byte stores).
@@ -192,13 +251,12 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         return;
     }
     using SH = PShape<HD, TN>;
-    constexpr int Q_BYTES = SH::Q_BYTES, KV_TILE_BYTES = SH::KV_TILE_BYTES, P_BYTES = SH::P_BYTES;
-    constexpr int KV_LINE_TILE = SH::KV_LINE_TILE;
+    constexpr int Q_BYTES = SH::Q_BYTES, KV_TILE_BYTES = SH::KV_TILE_BYTES;
+    constexpr int KV_LINE_TILE = SH::KV_LINE_TILE, KV_STAGES = SH::KV_STAGES;
     constexpr int HALVES = HD / 64;                                   // sub-tiles of 64 columns in a row of Q, K, V
     unsigned char* q_tile = pt_smem_raw;
     unsigned char* kv_tiles = q_tile + Q_BYTES;                       // [stage][K|V]
-    unsigned char* p_tile = kv_tiles + KV_STAGES * 2 * KV_TILE_BYTES;
-    PCtrl* ctrl = reinterpret_cast<PCtrl*>(p_tile + P_BYTES);
+    PCtrl* ctrl = reinterpret_cast<PCtrl*>(kv_tiles + KV_STAGES * 2 * KV_TILE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nrep = nh / nkv;
@@ -237,7 +295,8 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
         }
         bar_init(&ctrl->s_full, 1);
         bar_init(&ctrl->s_empty, 4);
-        bar_init(&ctrl->p_full, 4);
+        bar_init(&ctrl->p_full[0], 4);
+        bar_init(&ctrl->p_full[1], 4);
         bar_init(&ctrl->o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -249,15 +308,21 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = ctrl->tmem_base;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u;
-    // warps 2-5: warp w reads TMEM lanes 32 (w % 4) .. + 31; a lane is a row of the tile
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128u, tmem_p = tmem_base + SH::P_COL;
+    // warps 4-7: warp w reads TMEM lanes 32 (w % 4) .. + 31; a lane is a row of the tile
     const int srow = (warp & 3) * 32 + lane;
     const uint32_t slane_addr = (uint32_t)((warp & 3) * 32) << 16;
     float m_ref = -INFINITY, l_run = 0.f;       // the reference of the row's exponentials so far, and their sum
     bool row_ok = true;
+    // The CTA starts with 128 registers a thread.  The first four warps need few and hand theirs to
+    // the softmax warps, which hold a row of 128 scores each and want room beside it to keep several
+    // exponentials in flight (with 168 registers for everybody a block took 3700 cycles of a lone
+    // CTA, with 206 it took 2900).
     pdl_wait();             // q and this portion's keys come from the kernels before
 
-    if (warp == 0) {
+    if (warp < PT_SOFTMAX_WARP0) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 0) {
         // producer.  A block of keys is 128 / page_size pages for K and as many for V, each a copy
         // of its own: the lanes of the warp issue them side by side (one lane issuing sixteen
         // copies of 2 KB a block was what bounded the kernel).
@@ -300,8 +365,12 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             if (it < n_blk && !load_tile(it, false)) break;
             if (it >= 1 && !load_tile(it - 1, true)) break;
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
+      } else if (warp == 1) {
+        // The whole warp walks the loop and waits; one lane issues.  (With the loop inside
+        // `if (lane == 0)` a product's eight instructions took 800 cycles to issue and every wait on
+        // a barrier that was long complete 250: the block's chain P ready -> P V done was 1200
+        // cycles for 256 of tensor work.)
+        {
             bool ok = bar_wait(&ctrl->q_full, 0, &ctrl->abort);
             uint64_t qdesc[HALVES];
 #pragma unroll
@@ -312,46 +381,72 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                 // the softmax warps have taken the scores of the block before out of tensor memory
                 if (it > 0 && !bar_wait(&ctrl->s_empty, (it - 1) & 1, &ctrl->abort)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned char* kt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES;
+                if (lane == 0) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    // four k-steps of 32 bytes inside a sub-tile of 64 columns, then the next sub-tile
-                    const uint64_t kdesc = smem_desc_sw128(kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + (size_t)(k / 4) * KV_LINE_TILE);
-                    umma_bf16(tmem_s, qdesc[k / 4] + (uint64_t)((k % 4) * 32 >> 4), kdesc + (uint64_t)((k % 4) * 32 >> 4),
-                              SH::IDESC_S, k != 0 ? 1u : 0u);
+                    for (int k = 0; k < HD / 16; ++k) {
+                        // four k-steps of 32 bytes inside a sub-tile of 64 columns, then the next sub-tile
+                        const uint64_t kdesc = smem_desc_sw128(kt + (size_t)(k / 4) * KV_LINE_TILE);
+                        umma_bf16(tmem_s, qdesc[k / 4] + (uint64_t)((k % 4) * 32 >> 4), kdesc + (uint64_t)((k % 4) * 32 >> 4),
+                                  SH::IDESC_S, k != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&ctrl->s_full);
+                    umma_commit(&ctrl->k_empty[s]);
                 }
-                umma_commit(&ctrl->s_full);
-                umma_commit(&ctrl->k_empty[s]);
+                __syncwarp();
                 return true;
             };
             if (ok && n_blk > 0) ok = issue_s(0);
             for (int it = 0; it < n_blk && ok; ++it) {
                 const int s = it % KV_STAGES;
                 if (it + 1 < n_blk && !issue_s(it + 1)) break;         // the next block's scores, behind this block's softmax
-                if (!bar_wait(&ctrl->p_full, it & 1, &ctrl->abort)) break;
+                // the values have been there for a while; P is what the product waits for
                 if (!bar_wait(&ctrl->v_full[s], (it / KV_STAGES) & 1, &ctrl->abort)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned char* vt = kv_tiles + (size_t)s * 2 * KV_TILE_BYTES + KV_TILE_BYTES;
+                // O += P V in two bursts: the first half of the keys while the softmax warps are in the
+                // exponentials of the second (a burst costs 300 cycles before its first instruction
+                // is through and 50 an instruction; after the last exponential only four are left)
+                bool fine = true;
 #pragma unroll
-                for (int k = 0; k < TN / 16; ++k) {
-                    // P: swizzled sub-tiles of 64 keys, 32 bytes a step inside one; V: 16 keys = 2 KB further
-                    // in each of its sub-tiles of 64 head dimensions
-                    const uint64_t pdesc = smem_desc_sw128(p_tile + (size_t)(k / 4) * LINE_TILE) + (uint64_t)((k % 4) * 32 >> 4);
-                    const uint64_t vdesc = HALVES == 1 ? smem_desc_sw128(vt + (size_t)k * 16 * 128)
-                                                       : smem_desc_sw128_mn(vt + (size_t)k * 16 * 128, (uint32_t)KV_LINE_TILE);
-                    umma_bf16(tmem_o, pdesc, vdesc, SH::IDESC_PV, (it | k) != 0 ? 1u : 0u);     // O accumulates over the blocks
+                for (int hf = 0; hf < 2; ++hf) {
+                    if (!bar_wait(&ctrl->p_full[hf], it & 1, &ctrl->abort)) { fine = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (lane == 0) {
+#pragma unroll
+                        for (int k = hf * (TN / 32); k < (hf + 1) * (TN / 32); ++k) {
+                            // P: 16 keys are 8 columns of tensor memory; V: 16 keys = 2 KB further in each of
+                            // its sub-tiles of 64 head dimensions
+                            const uint64_t vdesc = HALVES == 1 ? smem_desc_sw128(vt + (size_t)k * 16 * 128)
+                                                               : smem_desc_sw128_mn(vt + (size_t)k * 16 * 128, (uint32_t)KV_LINE_TILE);
+                            umma_bf16_ts(tmem_o, tmem_p + (uint32_t)(k * 8), vdesc, SH::IDESC_PV, (it | k) != 0 ? 1u : 0u);   // O accumulates over the blocks
+                        }
+                        if (hf == 1) {
+                            umma_commit(&ctrl->o_full);
+                            umma_commit(&ctrl->v_empty[s]);
+                        }
+                    }
+                    __syncwarp();
                 }
-                umma_commit(&ctrl->o_full);
-                umma_commit(&ctrl->v_empty[s]);
+                if (!fine) break;
+                __syncwarp();
             }
         }
+      }
+      if (splits > 1) {         // the two meetings of the cluster around the exchange of rows (below)
+          __syncwarp();
+          cluster_sync_all();
+          __syncwarp();
+          cluster_sync_all();
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // softmax and output
         const int r = srow;
         const int pos = pos0 + (srow & 63);
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
         const uint32_t lane_addr = slane_addr;
         const float scale_log2 = scale * 1.4426950408889634f;
-        unsigned char* prow = p_tile + (size_t)r * 128;          // this row's 128-byte line in each half
+        const uint32_t tmem_p_row = tmem_p + lane_addr;
         bool ok = true;
         for (int it = 0; it < n_blk; ++it) {
             const int key0 = (blk0 + it * splits) * TN;
@@ -381,11 +476,11 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                     max_of_chunk<true>(s3, 3, kmin, kmax, mx);
                 }
             } else {
-                max_of_chunk<false>(s0, 0, kmin, kmax, mx);
-                max_of_chunk<false>(s1, 1, kmin, kmax, mx);
+                max_of_chunk3(s0, mx);
+                max_of_chunk3(s1, mx);
                 if constexpr (TN > 64) {
-                    max_of_chunk<false>(s2, 2, kmin, kmax, mx);
-                    max_of_chunk<false>(s3, 3, kmin, kmax, mx);
+                    max_of_chunk3(s2, mx);
+                    max_of_chunk3(s3, mx);
                 }
             }
             const float m_new = fmaxf(m_ref, mx * scale_log2);
@@ -399,6 +494,8 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             // the product P V of the block before: P may be overwritten and O rescaled once it is done
+            // (handing the halves of P back one by one, each after its own part of the product, was
+            // measured: the waits it adds cost more than the wait it saves, 485 against 469 us at 8192)
             if (it > 0) {
                 ok = bar_wait(&ctrl->o_full, (it - 1) & 1, &ctrl->abort) && ok;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -414,125 +511,137 @@ __global__ __launch_bounds__(PT_THREADS, 2) void attn_prefill_tc_kernel(
                     tmem_st_wait();
                 }
             }
-            float lsum = 0.f;
-            if (need_mask) {
-                exp_of_chunk<true>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<true>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                if constexpr (TN > 64) {
-                    exp_of_chunk<true>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                    exp_of_chunk<true>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                }
-            } else {
-                exp_of_chunk<false>(s0, 0, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                exp_of_chunk<false>(s1, 1, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                if constexpr (TN > 64) {
-                    exp_of_chunk<false>(s2, 2, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                    exp_of_chunk<false>(s3, 3, kmin, kmax, scale_log2, m_use, prow, r, lsum);
-                }
-            }
-            l_run += lsum;
             // Slots of the last page past the context hold whatever was there before; a zero of P
             // times a NaN would still be a NaN, so those rows of V are cleared (thread r: key r of
-            // the block), once the tile has arrived
-            if (key0 + TN > ctx) ok = bar_wait(&ctrl->v_full[it % KV_STAGES], (it / KV_STAGES) & 1, &ctrl->abort) && ok;
-            if (r < TN && key0 + r >= ctx) {
+            // the block), once the tile has arrived and before any of P is handed over
+            if (key0 + TN > ctx) {
+                ok = bar_wait(&ctrl->v_full[it % KV_STAGES], (it / KV_STAGES) & 1, &ctrl->abort) && ok;
+                if (r < TN && key0 + r >= ctx) {
 #pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf) {
-                    uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES +
-                                                           (size_t)hf * KV_LINE_TILE + (size_t)r * 128);
+                    for (int hf = 0; hf < HALVES; ++hf) {
+                        uint4* vrow = reinterpret_cast<uint4*>(kv_tiles + (size_t)(it % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES +
+                                                               (size_t)hf * KV_LINE_TILE + (size_t)r * 128);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+                        for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // for the tensor core's reads of V
+            }
+            // P goes to tensor memory in two halves of the block's keys, each handed to the product
+            // as soon as it is complete (O, if it was rescaled, is back there before the first)
+            const uint64_t scale2 = pair_of(scale_log2), neg_m2 = pair_of(-m_use);
+            uint64_t lsum2 = 0ull;
+            auto hand_over = [&](int half) {
+                tmem_st_wait();
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) bar_arrive(&ctrl->p_full[half]);
+            };
+            if (need_mask) {
+                exp_of_chunk<true>(s0, 0, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                if constexpr (TN == 64) hand_over(0);
+                exp_of_chunk<true>(s1, 1, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                if constexpr (TN > 64) {
+                    hand_over(0);
+                    exp_of_chunk<true>(s2, 2, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                    exp_of_chunk<true>(s3, 3, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                }
+            } else {
+                exp_of_chunk<false>(s0, 0, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                if constexpr (TN == 64) hand_over(0);
+                exp_of_chunk<false>(s1, 1, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                if constexpr (TN > 64) {
+                    hand_over(0);
+                    exp_of_chunk<false>(s2, 2, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
+                    exp_of_chunk<false>(s3, 3, kmin, kmax, scale2, neg_m2, tmem_p_row, lsum2);
                 }
             }
-            // P is in shared memory for the tensor core, O (if rescaled) back in tensor memory
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) bar_arrive(&ctrl->p_full);
+            l_run += sum_of_pair(lsum2);
+            hand_over(1);
         }
         if (n_blk > 0) {
             ok = bar_wait(&ctrl->o_full, (n_blk - 1) & 1, &ctrl->abort) && ok;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         row_ok = ok;
-    }
-    // the row's place in the output: head (srow / 64) of the pair, token (srow % 64) of the tile
-    const bool srow_valid = (srow & 63) < n_valid && (srow < 64 || two);
-    bf16* sorow = out + ((size_t)(q_start + t0 + (srow & 63)) * nh + (srow < 64 ? head0 : head1)) * HD;
-    if (splits == 1) {
-        if (warp >= 2 && n_blk > 0) store_row<HD>(tmem_o + slane_addr, 1.0f / l_run, row_ok && srow_valid, sorow);
-    } else {
-        // The CTAs of the cluster took the blocks of keys in turn.  Once all their products are done
-        // (the tiles in shared memory are free), ranks 1.. send their rows (64 unnormalised sums,
-        // the reference of the exponentials and their sum) into rank 0's tiles; rank 0 brings them
-        // to one reference in the order of the ranks, adds, normalises and stores.
-        constexpr int ROW_F = SH::ROW_F;               // floats a row in the exchange area (16-byte aligned rows)
-        float* xchg = reinterpret_cast<float*>(pt_smem_raw);
-        __syncwarp();
-        cluster_sync_all();
-        if (warp >= 2 && rank > 0) {
-            float* dst = xchg + ((size_t)(rank - 1) * TM + srow) * ROW_F;
-            uint32_t raddr;
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(dst)), "r"(0));
-#pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t v[32];
-                if (n_blk > 0) {
-                    tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;            // no block of its own: nothing was accumulated
+        // the row's place in the output: head (srow / 64) of the pair, token (srow % 64) of the tile
+        const bool srow_valid = (srow & 63) < n_valid && (srow < 64 || two);
+        bf16* sorow = out + ((size_t)(q_start + t0 + (srow & 63)) * nh + (srow < 64 ? head0 : head1)) * HD;
+        if (splits == 1) {
+            if (n_blk > 0) store_row<HD>(tmem_o + slane_addr, 1.0f / l_run, row_ok && srow_valid, sorow);
+        } else {
+            // The CTAs of the cluster took the blocks of keys in turn.  Once all their products are done
+            // (the tiles in shared memory are free), ranks 1.. send their rows (64 unnormalised sums,
+            // the reference of the exponentials and their sum) into rank 0's tiles; rank 0 brings them
+            // to one reference in the order of the ranks, adds, normalises and stores.
+            constexpr int ROW_F = SH::ROW_F;               // floats a row in the exchange area (16-byte aligned rows)
+            float* xchg = reinterpret_cast<float*>(pt_smem_raw);
+            __syncwarp();
+            cluster_sync_all();
+            if (rank > 0) {
+                float* dst = xchg + ((size_t)(rank - 1) * TM + srow) * ROW_F;
+                uint32_t raddr;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(dst)), "r"(0));
+    #pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t v[32];
+                    if (n_blk > 0) {
+                        tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
+                    } else {
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;            // no block of its own: nothing was accumulated
+                    }
+    #pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr + (uint32_t)((c * 32 + i) * 4)),
+                                     "r"(v[i]), "r"(v[i + 1]), "r"(v[i + 2]), "r"(v[i + 3]) : "memory");
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr + (uint32_t)((c * 32 + i) * 4)),
-                                 "r"(v[i]), "r"(v[i + 1]), "r"(v[i + 2]), "r"(v[i + 3]) : "memory");
+                asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(raddr + (uint32_t)(HD * 4)),
+                             "r"(__float_as_uint(m_ref)), "r"(__float_as_uint(row_ok ? l_run : __int_as_float(0x7fc00000))) : "memory");
             }
-            asm volatile("st.shared::cluster.v2.b32 [%0], {%1, %2};" ::"r"(raddr + (uint32_t)(HD * 4)),
-                         "r"(__float_as_uint(m_ref)), "r"(__float_as_uint(row_ok ? l_run : __int_as_float(0x7fc00000))) : "memory");
-        }
-        __syncwarp();
-        cluster_sync_all();
-        if (warp >= 2 && rank == 0) {
-            float m = m_ref;
-            for (int k = 1; k < splits; ++k) m = fmaxf(m, xchg[((size_t)(k - 1) * TM + srow) * ROW_F + HD]);
-            const float f0 = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m);
-            float l = l_run * f0;
-            float fk[3] = {0.f, 0.f, 0.f};
-#pragma unroll
-            for (int k = 1; k < 4; ++k) {
-                if (k < splits) {
-                    const float* src = xchg + ((size_t)(k - 1) * TM + srow) * ROW_F;
-                    fk[k - 1] = src[HD] == -INFINITY ? 0.f : ex2_approx(src[HD] - m);
-                    l += src[HD + 1] * fk[k - 1];
-                }
-            }
-            const float inv = 1.0f / l;
-#pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t v[32];
-                if (n_blk > 0) {
-                    tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f0);
-#pragma unroll
+            __syncwarp();
+            cluster_sync_all();
+            if (rank == 0) {
+                float m = m_ref;
+                for (int k = 1; k < splits; ++k) m = fmaxf(m, xchg[((size_t)(k - 1) * TM + srow) * ROW_F + HD]);
+                const float f0 = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m);
+                float l = l_run * f0;
+                float fk[3] = {0.f, 0.f, 0.f};
+    #pragma unroll
                 for (int k = 1; k < 4; ++k) {
-                    if (k >= splits) continue;
-                    const float4* src = reinterpret_cast<const float4*>(xchg + ((size_t)(k - 1) * TM + srow) * ROW_F + c * 32);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 o = src[i];
-                        v[4 * i] = __float_as_uint(fmaf(o.x, fk[k - 1], __uint_as_float(v[4 * i])));
-                        v[4 * i + 1] = __float_as_uint(fmaf(o.y, fk[k - 1], __uint_as_float(v[4 * i + 1])));
-                        v[4 * i + 2] = __float_as_uint(fmaf(o.z, fk[k - 1], __uint_as_float(v[4 * i + 2])));
-                        v[4 * i + 3] = __float_as_uint(fmaf(o.w, fk[k - 1], __uint_as_float(v[4 * i + 3])));
+                    if (k < splits) {
+                        const float* src = xchg + ((size_t)(k - 1) * TM + srow) * ROW_F;
+                        fk[k - 1] = src[HD] == -INFINITY ? 0.f : ex2_approx(src[HD] - m);
+                        l += src[HD + 1] * fk[k - 1];
                     }
                 }
-                if (row_ok && srow_valid && l == l) store_chunk(v, inv, sorow + c * 32);
+                const float inv = 1.0f / l;
+    #pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t v[32];
+                    if (n_blk > 0) {
+                        tmem_ld32(tmem_o + slane_addr + (uint32_t)(c * 32), v);
+                    } else {
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    }
+    #pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f0);
+    #pragma unroll
+                    for (int k = 1; k < 4; ++k) {
+                        if (k >= splits) continue;
+                        const float4* src = reinterpret_cast<const float4*>(xchg + ((size_t)(k - 1) * TM + srow) * ROW_F + c * 32);
+    #pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 o = src[i];
+                            v[4 * i] = __float_as_uint(fmaf(o.x, fk[k - 1], __uint_as_float(v[4 * i])));
+                            v[4 * i + 1] = __float_as_uint(fmaf(o.y, fk[k - 1], __uint_as_float(v[4 * i + 1])));
+                            v[4 * i + 2] = __float_as_uint(fmaf(o.z, fk[k - 1], __uint_as_float(v[4 * i + 2])));
+                            v[4 * i + 3] = __float_as_uint(fmaf(o.w, fk[k - 1], __uint_as_float(v[4 * i + 3])));
+                        }
+                    }
+                    if (row_ok && srow_valid && l == l) store_chunk(v, inv, sorow + c * 32);
+                }
             }
         }
     }

@@ -21,9 +21,9 @@ NEAR_TIE = 0.02
 # With random weights the rounding errors at two candidates are independent, and top-2 margins of a
 # few hundredths are common, so the margin rule above needs the size of the noise beside it.  The
 # noise is measured on every row (the rms error over the whole vocabulary: 0.0094 of the logits'
-# spread at the 1B sizes, 0.0112 at the 3B sizes in bfloat16, 3e-6 and 4e-6 in float32, the same for whole prompts, single tokens and
-# mixed steps) and bounded; a choice may then differ where the margin is below four times that
-# row's own noise.  A fault at a row raises its noise past the bound long before it reaches 0.15.
+# spread at the 1B sizes and 0.0112 at the 3B sizes in bfloat16, 3e-6 and 4e-6 in float32, the same
+# for whole prompts, single tokens and mixed steps) and bounded; a choice may then differ where
+# the margin is below four times that row's own noise.  A fault at a row raises its noise past the bound long before it reaches 0.15.
 ROW_NOISE = {"float32": 1e-5, "bfloat16": 0.015}      # rms error of a row / spread of its logits
 
 
