@@ -47,7 +47,16 @@
 //   (Measured and dropped: four heads a CTA with two softmax groups over one ring of tiles and one
 //   issuing thread, 627 us at 8192, the thread's bursts one after the other being the bound; the
 //   same with the two groups taking turns at the exponentials, 672 us; handing the halves of P
-//   back one by one after their own bursts instead of waiting for the whole product, 485 us.)
+//   back one by one after their own bursts instead of waiting for the whole product, 485 us; eight
+//   softmax warps, two threads a row that both read the whole row for the maximum and keep a half
+//   each, 512 us: both halves of P are then ready at the same moment, the product's two bursts
+//   follow the last exponential one after the other, and the wait for them grows from 400 to 900
+//   cycles, more than four warps a scheduler win at the special-function unit.)
+//   What is left of a block's 3040 cycles: the exponentials 1900 (the unit's floor for the two
+//   CTAs is 2048 a block of both), and the chain last exponential -> P handed over -> second burst
+//   (four instructions, their commit 200 cycles, done 170 later) -> the next block's first
+//   exponential, about 1000 cycles of which the next block's maximum hides 600.  P cannot be kept
+//   twice to take the chain out of the loop: S, O and P fill the CTA's 256 columns.
 //
 // Head size 128 is the same kernel with blocks of 64 keys, so that the tiles are as large and two
 // CTAs still fit: a row of Q, K or V is two 128-byte lines, kept as two swizzled sub-tiles of 64
