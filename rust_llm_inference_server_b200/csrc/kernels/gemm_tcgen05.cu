@@ -23,6 +23,7 @@
 // (rlis_gemm_tcgen05_error), lets every role run to its end without further waiting, and the
 // CTA still frees its tensor memory before it returns.
 #include "tcgen05_utils.cuh"
+#include "gemm_epilogue.cuh"
 #include <math.h>
 
 namespace {
@@ -138,48 +139,7 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
                 tmem_ld32(tmem_acc + (uint32_t)(cb * 32), r);
                 const int col = n0 + cb * 32;
                 if (!ok || row >= M || col >= N) continue;
-                if (EPI == 0) {
-                    bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * N + col;
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        if (col + v * 8 >= N) break;
-                        uint4 pk;
-                        pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                        pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                        pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                        pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                        *reinterpret_cast<uint4*>(o + v * 8) = pk;
-                    }
-                } else if (EPI == 1) {
-                    bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * (N >> 1) + (col >> 1);
-                    float res[16];
-#pragma unroll
-                    for (int tt = 0; tt < 4; ++tt)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float gt = __uint_as_float(r[tt * 8 + j]), up = __uint_as_float(r[tt * 8 + 4 + j]);
-                            res[tt * 4 + j] = gt / (1.0f + expf(-gt)) * up;
-                        }
-#pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        if (col + v * 16 >= N) break;
-                        uint4 pk;
-                        pk.x = pack_bf16(res[v * 8 + 0], res[v * 8 + 1]);
-                        pk.y = pack_bf16(res[v * 8 + 2], res[v * 8 + 3]);
-                        pk.z = pack_bf16(res[v * 8 + 4], res[v * 8 + 5]);
-                        pk.w = pack_bf16(res[v * 8 + 6], res[v * 8 + 7]);
-                        *reinterpret_cast<uint4*>(o + v * 8) = pk;
-                    }
-                } else {
-                    float* o = reinterpret_cast<float*>(y) + (size_t)row * N + col;
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        if (col + v * 4 >= N) break;
-                        *reinterpret_cast<float4*>(o + v * 4) = make_float4(
-                            __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
-                            __uint_as_float(r[v * 4 + 3]));
-                    }
-                }
+                store_sums32<EPI>(r, y, row, col, N);
             }
             // this warp has read its lanes of the buffer: hand it back to the product warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -198,6 +158,8 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
 
 }  // namespace
 
+#include "gemm_tcgen05_pair.cuh"
+
 // 0 if no bounded wait of the tcgen05 product ever ran out on the current device.
 extern "C" int rlis_gemm_tcgen05_error(void) {
     return tc::read_error_word();
@@ -213,6 +175,8 @@ extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, i
     if (epilogue == 1 && (N & 15) != 0) return RLIS_ERR_UNSUPPORTED;   // rows of N / 2 bf16 must stay 16-byte aligned
     if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
+    // more than one tile of rows: two SMs to a tile of 256 x 256
+    if (g_pair != 0 && M > BM) return launch_gemm_pair(x, W, y, M, N, K, epilogue, stream);
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, x, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return RLIS_ERR_UNSUPPORTED;
     static bool attr_done = false;

@@ -22,9 +22,11 @@ extern "C" int rlis_get_pdl(void) { return g_rlis_pdl; }
 //   decode_cluster   0 / 1     merge decode attention's pieces inside a cluster where possible
 //   decode_tma       0 / 1     fetch decode attention's keys by bulk tensor copies where possible
 //   prefill_splits   0,1,2,4   CTAs that share a tile's keys in the tcgen05 prefill attention (0: automatic)
+//   gemm_pair        -1 / 0    two SMs to a tile in the tcgen05 product of many rows (-1: where it applies)
 //   filtered_cluster 0 / 1     the cluster kernel of top-k / top-p sampling where the vocabulary fits
 extern "C" void rlis_stream_gemm_set_target(int);
 extern "C" void rlis_stream_gemm_set_min_stages(int);
+extern "C" void rlis_gemm_tcgen05_set_pair(int);
 extern "C" void rlis_attention_decode_set_stages(int);
 extern "C" void rlis_attention_decode_set_cluster(int);
 extern "C" void rlis_attention_decode_set_tma(int);
@@ -40,6 +42,7 @@ extern "C" int rlis_debug_set(const char* name, int value) {
     else if (!strcmp(name, "decode_cluster")) rlis_attention_decode_set_cluster(value);
     else if (!strcmp(name, "decode_tma")) rlis_attention_decode_set_tma(value);
     else if (!strcmp(name, "prefill_splits")) rlis_attention_prefill_tc_set_splits(value);
+    else if (!strcmp(name, "gemm_pair")) rlis_gemm_tcgen05_set_pair(value);
     else if (!strcmp(name, "filtered_cluster")) rlis_sample_filtered_set_cluster(value);
     else return RLIS_ERR_UNSUPPORTED;
     return 0;

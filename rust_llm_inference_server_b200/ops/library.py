@@ -56,8 +56,8 @@ class KernelError(RuntimeError):
 
 
 # Switches for measurements and tests; nothing in the engine sets one.  In the library
-# (csrc/kernels/runtime_switches.cu): pdl, stream_ctas, decode_stages, decode_cluster, decode_tma,
-# prefill_splits, filtered_cluster.  In Python (ops/__init__.py): fuse_norms, prefill_tcgen05, stream_rows.
+# (csrc/kernels/runtime_switches.cu): pdl, stream_ctas, stream_min_stages, decode_stages, decode_cluster,
+# decode_tma, prefill_splits, gemm_pair, filtered_cluster.  In Python (ops/__init__.py): fuse_norms, prefill_tcgen05, stream_rows.
 # `RLIS_DEBUG=name=value,name=value` in the environment sets them when the library is loaded.
 PYTHON_SWITCHES: dict = {}
 

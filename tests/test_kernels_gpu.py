@@ -192,19 +192,30 @@ def test_streaming_product_with_gating_and_interleaved_gating_kernel(I, K, M):
         assert bool(((out.double().cpu() - w2).abs() <= 2.0 ** -7 * w2.abs() + 1e-5).all())
 
 
+@pytest.mark.parametrize("pair", [True, False])
 @pytest.mark.parametrize("shape,epilogue", [((128, 256, 64), "float32"), ((128, 256, 512), "float32"), ((300, 520, 200), "plain"),
                                             ((129, 264, 8), "float32"), ((333, 1008, 96), "swiglu4"),
                                             ((2048, 2048, 2048), "plain"), ((1024, 4096, 2048), "swiglu4"),
-                                            ((700, 1536, 8192), "plain")])
-def test_tcgen05_product_with_its_epilogues(shape, epilogue):
+                                            ((700, 1536, 8192), "plain"), ((256, 256, 64), "plain"),
+                                            ((2048 + 37, 19 * 256 + 24, 448), "plain"), ((40 * 256 + 1, 512, 72), "float32")])
+def test_tcgen05_product_with_its_epilogues(shape, epilogue, pair):
     """The TMA-fed tensor-memory GEMM against a float32 product: whole tiles, ragged M, N and K,
-    many tiles a CTA (both accumulator buffers in use), and the SwiGLU epilogue."""
+    many tiles a CTA (both accumulator buffers in use, the ring of stages walked several times),
+    and the SwiGLU epilogue; with two SMs to a tile of 256 x 256 (more than 128 rows) and with one
+    CTA to a tile of 128 x 256, whose results are the same bits."""
     from rust_llm_inference_server_b200 import ops
     M, N, K = shape
     torch.manual_seed(M + N)
     x, w = torch.randn(M, K).bfloat16(), (torch.randn(N, K) * 0.05).bfloat16()
-    got = ops.gemm_tcgen05(dev(x), dev(w), epilogue).float().cpu()
-    ops.check_device_errors()                      # no bounded wait ran out
+    ops.debug_set("gemm_pair", -1 if pair else 0)
+    try:
+        got = ops.gemm_tcgen05(dev(x), dev(w), epilogue).float().cpu()
+        ops.check_device_errors()                      # no bounded wait ran out
+        if pair:
+            ops.debug_set("gemm_pair", 0)
+            assert torch.equal(got, ops.gemm_tcgen05(dev(x), dev(w), epilogue).float().cpu())
+    finally:
+        ops.debug_set("gemm_pair", -1)
     want = (x.double() @ w.double().t())
     if epilogue == "swiglu4":
         r = want.view(M, -1, 2, 4)
