@@ -56,7 +56,9 @@
 //   CTAs is 2048 a block of both), and the chain last exponential -> P handed over -> second burst
 //   (four instructions, their commit 200 cycles, done 170 later) -> the next block's first
 //   exponential, about 1000 cycles of which the next block's maximum hides 600.  P cannot be kept
-//   twice to take the chain out of the loop: S, O and P fill the CTA's 256 columns.
+//   twice to take the chain out of the loop: S, O and P fill the CTA's 256 columns.  (Head size 128
+//   has the room, S 64 + P 2 x 32 + O 128, and it was measured: 733 -> 723 us at 8192 tokens, 58.4
+//   -> 57.2 at 2048; not kept.)
 //
 // Head size 128 is the same kernel with blocks of 64 keys, so that the tiles are as large and two
 // CTAs still fit: a row of Q, K or V is two 128-byte lines, kept as two swizzled sub-tiles of 64
