@@ -368,7 +368,9 @@ __global__ __launch_bounds__(S_THREADS) void stream_gemm_kernel(const __grid_con
                 for (int j = 0; j < 16; j += 4)
                     st_cluster_f32x4(dst + ((c * 16 + j) / 4) * (CHUNK_F * 4), r[j], r[j + 1], r[j + 2], r[j + 3], to);
             }
+            TL_STAMP(4);
             cluster_sync_all();                 // what was sent has arrived; nobody touches another CTA's memory from here on
+            TL_STAMP(5);
             // thread -> feature fi of the chunk and tokens tg, tg + 16, ...: the 8 features of a token are
             // neighbouring lanes (the SwiGLU pairs four lanes apart, 16-byte runs of y)
             const int tg = (int)threadIdx.x / CHUNK_F;
