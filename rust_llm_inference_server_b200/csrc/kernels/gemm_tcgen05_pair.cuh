@@ -149,7 +149,10 @@ __global__ __launch_bounds__(GP_THREADS) void gemm_tcgen05_pair_kernel(const __g
             // tensor work: the instructions queue behind the pipe, which is held up by shared memory,
             // 32 KB a block written by the copies and 32 KB read by the products at 128 bytes a
             // cycle.  The kernel with one CTA a tile moves 48 + 48 KB a block and runs at 68 %.
-            // Looking at the next stage's barrier ahead of the instructions changed nothing.)
+            // Looking at the next stage's barrier ahead of the instructions changed nothing.  Tiles
+            // of 192 columns, 128 of them in two rounds for a QKV product of 2048 x 3072 where tiles
+            // of 256 are 96 in two rounds: 30.7 against 31.3 us, the bytes a k-block moves through
+            // shared memory shrink by 15 % only.)
             int it = 0, t = 0;
             bool fine = true;
             for (int tile = pair; tile < num_tiles && fine && !ctrl->abort; tile += pairs, ++t) {
