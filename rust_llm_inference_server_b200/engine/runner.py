@@ -68,6 +68,7 @@ class StepContext:
         self.n_prefill_tiles = 0
         self.prefill_tiles = None                 # int32 [tiles, 2]: (batch entry, first token of the tile)
         self.n_wanted = 0                         # rows whose logits are asked for
+        self.wants_every_row = False              # ... and they are all the step's rows, in order
         self._views = None
         self._token_region = None
 
@@ -177,6 +178,7 @@ class ModelRunner:
             lens.append(n)
             T += n
         W = len(want_rows)
+        wants_every_row = W == T and want_rows == list(range(T))
         mb = self.max_blocks
         # layout of the int32 block: see the offsets below; every region starts 16-byte aligned
         o_tok = 0
@@ -245,6 +247,7 @@ class ModelRunner:
 
         st = StepContext(self, T, B)
         st.n_wanted = W
+        st.wants_every_row = wants_every_row
         st.q_lens = lens
         st.starts = starts
         st.state_slot_ids = h[o_ss:o_ss + B].tolist()

@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_config import read_config_json
+from ..ops import ScaledRows
 from ..config.registry import lookup_architecture
 from ..parts.base import Part, build_block, build_embedding, build_lm_head, build_norm
 from ..parts.spec import EmbeddingSpec, LMHeadSpec, ModelSpec
@@ -44,6 +45,7 @@ class Model:
         self.blocks = [build_block(ls, dtype, self.device) for ls in spec.layers]
         self.final_norm = build_norm(spec.final_norm, dtype, self.device)
         self.lm_head = build_lm_head(head, dtype, self.device)
+        self._tail = _Tail(self.final_norm, self.lm_head)
         self.calls = tuple(spec.order)
         self._plan_caches()
         # parts whose launch configuration depends on more than the step's shape
@@ -125,11 +127,18 @@ class Model:
         residual stream and the last pending delta; `logits` finishes chosen rows."""
         T = step.n_tokens
         resid = step.buffer("resid", (T, self.spec.hidden), torch.float32)
-        self.embedding.forward(step.token_ids, resid, step)
         delta = None
+        first = self.blocks[self.calls[0].layer] if self.calls else None
+        emb_fuses = getattr(self.embedding, "fuses_norms", None)
+        sink = first.entry_sink(resid, step) if (emb_fuses is not None and emb_fuses(step) and
+                                                 getattr(first, "chains_norms", False)) else None
+        if sink is not None:    # the first block's first norm is left to its first product
+            delta = self.embedding.forward(step.token_ids, resid, step, sink=sink)
+        else:
+            self.embedding.forward(step.token_ids, resid, step)
         for ci, call in enumerate(self.calls):
             blk = self.blocks[call.layer]
-            nxt = self.blocks[self.calls[ci + 1].layer] if ci + 1 < len(self.calls) else None
+            nxt = self.blocks[self.calls[ci + 1].layer] if ci + 1 < len(self.calls) else self._tail
             if getattr(blk, "chains_norms", False) and hasattr(nxt, "entry_sink"):
                 # the block may leave its last addition and the next block's first norm to the products around them
                 resid, delta = blk.forward(resid, delta, step, caches[call.cache], states[ci], call.writes_cache,
@@ -141,8 +150,27 @@ class Model:
     def logits(self, resid, delta, step, rows: torch.Tensor):
         """Final norm and LM head on the rows in `rows` (int32 indices into the step's tokens):
         float32 logits [len(rows), vocab] (crates/model/src/llama.rs:272-285)."""
+        if isinstance(delta, ScaledRows):       # the last block left the final norm to the head's product
+            return self.lm_head.forward(delta, step)
         h = self.final_norm.forward_rows(resid, delta, step, rows)
         return self.lm_head.forward(h, step)
+
+
+class _Tail:
+    """What follows the last block, asked as a block is asked for its `entry_sink`: the final norm's
+    sink, when the step wants the logits of all its rows in order (a decode step) and the head's
+    product takes the rows that come out of it.  The last block's last product then adds to the
+    residual stream itself and the final norm is no kernel of its own."""
+
+    def __init__(self, final_norm, lm_head):
+        self.final_norm, self.lm_head = final_norm, lm_head
+
+    def entry_sink(self, resid, step):
+        head_fuses = getattr(self.lm_head, "fuses_norms", None)
+        if not getattr(step, "wants_every_row", False) or head_fuses is None or not head_fuses(step):
+            return None
+        sink = getattr(self.final_norm, "sink", None)
+        return sink(resid, step) if sink is not None else None
 
 
 def build_model(config_json: dict, dtype, device="cuda") -> Model:

@@ -94,6 +94,27 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: 
     return out
 
 
+def embedding_sink(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float | None, sink):
+    """`embedding` for a step whose first norm is left to the product after it (`sink`, a
+    ResidualSink over `out`): also returns that norm's ScaledRows, bf16(row * weight) and the sums of
+    squares of every 128 features.  bfloat16 tables whose width is a multiple of 8."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _req(ids, "ids", torch.int32, (T,))
+    _req(table, "table", torch.bfloat16)
+    _req(out, "out", torch.float32, (T, H))
+    _req(sink.weight, "sink.weight", torch.float32, (H,))
+    if sink.resid.data_ptr() != out.data_ptr() or H % 8:
+        raise KernelError("embedding_sink: the sink is over another residual stream, or the width is no multiple of 8")
+    xn = torch.empty((T, H), dtype=torch.bfloat16, device=out.device)
+    partials = torch.empty(((H + 127) // 128, T), dtype=torch.float32, device=out.device)
+    check(lib().rlis_embedding_sink(ids.data_ptr(), table.data_ptr(), out.data_ptr(), sink.weight.data_ptr(),
+                                    xn.data_ptr(), partials.data_ptr(), T, H, V,
+                                    1.0 if scale is None else float(scale), _stream()), "embedding_sink")
+    _count("embedding.sink")
+    return ScaledRows(xn, partials, H, sink.eps)
+
+
 def logit_transform(logits: torch.Tensor, scale: float | None, soft_cap: float | None) -> torch.Tensor:
     """In place on float32 logits [R, V]: x <- x * scale, then x <- cap * tanh(x / cap) (each only
     where given)."""

@@ -22,6 +22,7 @@ LL = c_longlong
 # name -> argument types (the stream is always last)
 SIGNATURES = {
     "rlis_embedding": [P, P, P, I, I, I, F, I, P],
+    "rlis_embedding_sink": [P, P, P, P, P, P, I, I, I, F, P],
     "rlis_logit_transform": [P, I, I, LL, F, F, P],
     "rlis_attention_prefill_tile": [],
     "rlis_rmsnorm": [P, P, P, P, P, I, I, F, I, P],

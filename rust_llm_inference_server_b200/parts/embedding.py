@@ -26,8 +26,15 @@ class Embedding(TokenEmbedding):
     def load(self, src) -> None:
         self.weight = src.get(self.spec.weight, share=True).contiguous()
 
-    def forward(self, token_ids, out, step):
+    def fuses_norms(self, step) -> bool:
+        """True when `forward` takes a keyword `sink` in this step (the first block's first norm,
+        an `ops.ResidualSink` over `out`) and returns that norm's `ops.ScaledRows`."""
+        return self.weight.dtype == torch.bfloat16 and ops.fuses_norms(step.n_tokens, self.weight.dtype, self.spec.dim)
+
+    def forward(self, token_ids, out, step, sink=None):
         with span("embedding"):
+            if sink is not None:
+                return ops.embedding_sink(token_ids, self.weight, out, self.scale, sink)
             return ops.embedding(token_ids, self.weight, out, self.scale)
 
 
@@ -47,6 +54,10 @@ class LMHead(LogitsHead):
 
     def load(self, src) -> None:
         self.weight = src.get(self.spec.weight, share=True).contiguous()
+
+    def fuses_norms(self, step) -> bool:
+        """True when `forward` takes the `ops.ScaledRows` of the final norm in this step."""
+        return ops.fuses_norms(step.n_tokens, self.weight.dtype, self.spec.dim)
 
     def forward(self, h, step):
         with span("lm head"):

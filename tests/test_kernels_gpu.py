@@ -33,6 +33,34 @@ def test_embedding(dtype):
     assert torch.equal(out.cpu(), P.embedding(ids, table.float()))
 
 
+@pytest.mark.parametrize("hidden,scale", [(80, None), (2048, None), (328, 5.5)])
+def test_embedding_that_leaves_the_first_norm_to_the_product_after_it(hidden, scale):
+    """The lookup of a decode step: the float32 rows as `embedding` writes them, bf16(row * norm
+    weight), and the sums of squares of every 128 features; and the product that takes them gives
+    what the norm followed by the product gives."""
+    from rust_llm_inference_server_b200 import ops
+    torch.manual_seed(hidden)
+    table = torch.randn(301, hidden).bfloat16()
+    ids = torch.tensor([0, 300, 17, 17, 5, 9, 250], dtype=torch.int32)
+    w_norm = torch.randn(hidden)
+    eps = 1e-5
+    out = torch.empty(7, hidden, device="cuda")
+    rows = ops.embedding_sink(dev(ids), dev(table), out, scale, ops.ResidualSink(out, dev(w_norm), eps))
+    want = P.embedding(ids, table.float()) * (1.0 if scale is None else scale)
+    assert torch.equal(out.cpu(), want)
+    assert torch.equal(rows.x.cpu(), (want * w_norm).bfloat16())
+    tiles = (hidden + 127) // 128
+    assert rows.partials.shape == (tiles, 7)
+    for j in range(tiles):
+        ss = (want[:, j * 128:(j + 1) * 128].double() ** 2).sum(1)
+        assert bool(((rows.partials[j].cpu().double() - ss).abs() <= 1e-5 * ss + 1e-12).all())
+    w = (torch.randn(256, hidden) * 0.05).bfloat16()
+    got = ops.linear(rows, dev(w)).float().cpu()
+    ref = ops.linear(ops.rmsnorm(out.clone(), dev(w_norm), eps, torch.empty(7, hidden, dtype=torch.bfloat16, device="cuda")),
+                     dev(w)).float().cpu()
+    assert bool(((got - ref).abs() <= 2.0 ** -6 * ref.abs() + 2e-2).all())
+
+
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("hidden", [80, 1000, 4100])
 def test_rmsnorm_with_residual_and_rows(dtype, hidden):

@@ -54,7 +54,7 @@ def session(model_root, which, dtype, max_tokens, page_size=16):
 KERNELS_BF16 = {
     "D": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma",
           "gemm_tcgen05.swiglu4", "stream_gemm.sink", "stream_gemm.scaled", "stream_gemm.scaled.swiglu",
-          "rope_cache", "rmsnorm", "rmsnorm.rows", "embedding"],
+          "rope_cache", "rmsnorm", "rmsnorm.rows", "embedding", "embedding.sink"],
     "E": ["attention_prefill.tcgen05", "attention_decode.mma.tma", "attention_decode_qkv.mma.tma", "stream_gemm.sink",
           "stream_gemm.scaled"],
     "A": ["attention_generic", "attention_decode.cuda_core"],
